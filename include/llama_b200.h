@@ -270,21 +270,47 @@ B200_API const char* b200_batch_last_error(b200_batch* batch);   /* message of t
  *          floor(j / mask_size)); value blending across layers: the first layer with v_mix = B200_VMIX_SOURCE publishes its values
  *          of the step's tokens, a layer with B200_VMIX_BLEND caches (1 - l) v + l v_source, l = its scalar '.vmix'; output gate
  *          per channel or one sigmoid per head.
+ *   B200_MIX_LATENT_ATTN    softmax attention whose keys and values are read out of one low-rank latent per position
+ *          (b200_latent_attn_desc).  Queries: c_q = rmsnorm(W_dq h) * '.dq.norm', q = W_uq c_q, per head [dim plain | rot_dim rotated].
+ *          W_dkv h = [kv_rank | rot_dim]: the first part, rmsnorm * '.dkv.norm', is the latent c, the second, rotated, is one key part
+ *          shared by all heads; a slot's cache holds [c | rotated part] per position and nothing else.  Head n's plain key is
+ *          W_uk[n] c and its value W_uv[n] c; the kernels never form them per position: the query is carried into the latent
+ *          (W_uk[n]^T q_plain), scores and the weighted sum run over the cached rows as one shared K/V head of size kv_rank + rot_dim
+ *          / kv_rank, and W_uv[n] is applied to the summed latent.  score = (q_plain . k_plain + q_rot . k_rot) * scale; sliding window
+ *          of mask_size positions (0 = all earlier positions); rotation in the half-split layout (channel i with i + dims / 2) with the
+ *          frequencies of b200_rotary_desc; optional sigmoid gate per value channel from the mixer's input ('.g'); kv_from >= 0: the
+ *          layer has no W_dkv and reads the cache rows of that earlier layer (same kv_rank, rot_dim and rotation) with its own W_uk,
+ *          W_uv, queries and mask.
+ *   B200_MIX_STATE_SPACE    gated linear recurrence with a scalar decay per head (b200_state_space_desc): W_in h = [z | x | B | C | dt]
+ *          with inner = heads * vdim, B and C of groups * state; causal depthwise convolution ('.conv' [channels, taps], bias
+ *          '.conv.b') + SiLU over [x | B | C]; dt = softplus(dt + dt_bias); per head (group floor(head * groups / heads)):
+ *          S <- exp(-exp(A_log) dt) S + dt B x^T (S: state x vdim, f32, zero at the start), y = S^T C + D x; then y * silu(z), rms norm
+ *          in norm_groups equal parts times '.norm', W_o.  A slot's state block holds S and the last conv - 1 inputs of the convolution.
  * Feed-forward (ff_kind): B200_FF_RELU2 W_down relu(W_up h)^2 of width ff (none when ff = 0); B200_FF_GATED_GELU W_down (gelu_tanh(W_gate h)
  * * W_up h) of width ff; B200_FF_MOE: router logits W_router h in f32, the `top` largest are chosen and weighted by the softmax over
- * the chosen logits, experts W_down relu(W_up h)^2 of width expert_ff, plus an always-on expert of width shared_ff (0 = none).
+ * the chosen logits, experts W_down relu(W_up h)^2 of width expert_ff, plus an always-on expert of width shared_ff (0 = none);
+ * moe.route = B200_ROUTE_SOFTMAX_TOP: softmax over ALL experts, the `top` largest taken and weighted by their probability times
+ * route_scale, not renormalised; moe.act = B200_ACT_GELU: experts W_down gelu(W_up h) with the exact (erf) GELU.
  * Layer form (program): post_norm = 0: x += sublayer(norm(x)); post_norm = 1: x <- norm(residual_alpha * x + sublayer(x)), the
- * sublayers read x itself.  Norm weights are applied as (norm_weight_offset + w).
+ * sublayers read x itself.  Norm weights are applied as (norm_weight_offset + w).  norm_kind = B200_NORM_LAYER: the layer norms and
+ * the final norm subtract the mean first, (x - mean) / sqrt(var + eps) * w (no bias), instead of the RMS norm.
+ * streams >= 1: the residual is `streams` copies x_1 .. x_s of the embedding; sublayer q of a layer (1 mixer, 2 feed-forward) reads
+ * norm(sum_s hc<q>.in[s] x_s) and its output y updates all copies at once, x_t <- sum_s hc<q>.mix[s][t] x_s + residual_mult *
+ * hc<q>.out[t] * y; the head reads the sum of the copies.  A layer without 'l<i>.hc<q>.*' tensors takes in = out = 1, mix = identity
+ * (with one stream: x += residual_mult * y).
  * Embedding: row * embed_scale (+ sinusoidal position vector, pos_sinusoid); logits = head . norm(x) * logit_scale.
  * compute: 0 = bf16 weights and GEMM operands with f32 accumulation (residual stream, norms, softmax, gates and every recurrent
  * state stay f32), 1 = everything in f32 (FMA, no reduced-precision matrix mode). */
-enum { B200_MIX_WINDOW_MEMORY = 1, B200_MIX_GATED_DELTA = 2, B200_MIX_SOFTMAX_ATTN = 3 };
+enum { B200_MIX_WINDOW_MEMORY = 1, B200_MIX_GATED_DELTA = 2, B200_MIX_SOFTMAX_ATTN = 3, B200_MIX_LATENT_ATTN = 4, B200_MIX_STATE_SPACE = 5 };
 enum { B200_MASK_WINDOW = 0, B200_MASK_CHUNK = 1 };
 enum { B200_QKNORM_NONE = 0, B200_QKNORM_HEAD_WEIGHT = 1, B200_QKNORM_WHOLE_WEIGHT = 2, B200_QKNORM_HEAD_UNIT = 3 };
 enum { B200_GATE_NONE = 0, B200_GATE_CHANNEL = 1, B200_GATE_HEAD = 2 };
 enum { B200_VMIX_NONE = 0, B200_VMIX_SOURCE = 1, B200_VMIX_BLEND = 2 };
 enum { B200_FF_RELU2 = 0, B200_FF_GATED_GELU = 1, B200_FF_MOE = 2 };
 enum { B200_COMPUTE_BF16 = 0, B200_COMPUTE_F32 = 1 };
+enum { B200_NORM_RMS = 0, B200_NORM_LAYER = 1 };
+enum { B200_ACT_RELU2 = 0, B200_ACT_GELU = 1 };
+enum { B200_ROUTE_TOP_SOFTMAX = 0, B200_ROUTE_SOFTMAX_TOP = 1 };
 enum { B200_TYPE_BF16 = 30 };   /* ggml's id; accepted by layer-program contexts only */
 typedef struct b200_window_attn_desc {
     int32_t heads, kv_heads, dim, vdim;
@@ -314,7 +340,31 @@ typedef struct b200_softmax_attn_desc {
 } b200_softmax_attn_desc;
 typedef struct b200_moe_desc {
     int32_t experts, top, expert_ff, shared_ff;
+    int32_t act;                     /* B200_ACT_* of the experts */
+    int32_t route;                   /* B200_ROUTE_* */
+    float route_scale;               /* B200_ROUTE_SOFTMAX_TOP: factor on the chosen probabilities */
 } b200_moe_desc;
+/* Rotary frequencies: f_i = base^(-2i / dims), i < dims / 2.  yarn_factor > 0 stretches long wavelengths: with
+ * d(t) = dims ln(yarn_original / (2 pi t)) / (2 ln base), lo = max(floor(d(yarn_fast)), 0), hi = min(ceil(d(yarn_slow)), dims - 1) and
+ * ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1) the frequency is f_i / yarn_factor * ramp_i + f_i (1 - ramp_i), and cos and sin
+ * are both multiplied by 0.1 ln(yarn_factor) + 1. */
+typedef struct b200_rotary_desc {
+    int32_t dims;                    /* rotated channels at the start of the rotated part (even) */
+    float base;
+    float yarn_factor, yarn_original, yarn_fast, yarn_slow;
+} b200_rotary_desc;
+typedef struct b200_latent_attn_desc {
+    int32_t heads, dim, rot_dim, vdim;   /* per head: dim plain + rot_dim rotated query / key channels, vdim value channels */
+    int32_t q_rank, kv_rank;
+    int32_t mask_size;               /* sliding window; 0 = every earlier position */
+    float scale;
+    b200_rotary_desc rot;
+    int32_t kv_from;                 /* -1: own W_dkv and cache rows; j: the rows of layer j */
+    int32_t out_gate;                /* B200_GATE_NONE or B200_GATE_CHANNEL ('.g': [heads * vdim, width]) */
+} b200_latent_attn_desc;
+typedef struct b200_state_space_desc {
+    int32_t heads, vdim, state, groups, conv, norm_groups;
+} b200_state_space_desc;
 typedef struct b200_layer_desc {
     int32_t mixer;                   /* B200_MIX_* */
     b200_window_attn_desc attn;      /* WINDOW_MEMORY */
@@ -325,6 +375,8 @@ typedef struct b200_layer_desc {
     b200_softmax_attn_desc sattn;    /* SOFTMAX_ATTN */
     int32_t ff_kind;                 /* B200_FF_* */
     b200_moe_desc moe;               /* B200_FF_MOE */
+    b200_latent_attn_desc latent;    /* LATENT_ATTN */
+    b200_state_space_desc ssd;       /* STATE_SPACE */
 } b200_layer_desc;
 typedef struct b200_program_desc {
     int32_t width, vocab, n_layers;
@@ -336,6 +388,9 @@ typedef struct b200_program_desc {
     int32_t post_norm;                          /* 1 = norm after the residual sum (see "Layer form") */
     float residual_alpha;                       /* post_norm: weight of x in the sum */
     float norm_weight_offset;                   /* norm weights are stored minus this (0 or 1) */
+    int32_t norm_kind;                          /* B200_NORM_* of the layer norms and the final norm */
+    int32_t streams;                            /* 0: one residual stream in the forms above; >= 1: that many copies (see "streams") */
+    float residual_mult;                        /* streams >= 1: factor on every sublayer's output */
 } b200_program_desc;
 B200_API int b200_ctx_create_layers(const b200_program_desc* prog, const b200_layer_desc* layers, int device, b200_ctx** out);
 /* One batch of token runs: run i continues sequence slot seqs[i] with lens[i] tokens (concatenated in `tokens`).  want_rows are

@@ -115,14 +115,34 @@ class SoftmaxAttnDesc(C.Structure):
 
 class MoeDesc(C.Structure):
     """b200_moe_desc"""
-    _fields_ = [("experts", C.c_int32), ("top", C.c_int32), ("expert_ff", C.c_int32), ("shared_ff", C.c_int32)]
+    _fields_ = [("experts", C.c_int32), ("top", C.c_int32), ("expert_ff", C.c_int32), ("shared_ff", C.c_int32), ("act", C.c_int32),
+                ("route", C.c_int32), ("route_scale", C.c_float)]
+
+
+class RotaryDesc(C.Structure):
+    """b200_rotary_desc"""
+    _fields_ = [("dims", C.c_int32), ("base", C.c_float), ("yarn_factor", C.c_float), ("yarn_original", C.c_float),
+                ("yarn_fast", C.c_float), ("yarn_slow", C.c_float)]
+
+
+class LatentAttnDesc(C.Structure):
+    """b200_latent_attn_desc"""
+    _fields_ = [("heads", C.c_int32), ("dim", C.c_int32), ("rot_dim", C.c_int32), ("vdim", C.c_int32), ("q_rank", C.c_int32),
+                ("kv_rank", C.c_int32), ("mask_size", C.c_int32), ("scale", C.c_float), ("rot", RotaryDesc), ("kv_from", C.c_int32),
+                ("out_gate", C.c_int32)]
+
+
+class StateSpaceDesc(C.Structure):
+    """b200_state_space_desc"""
+    _fields_ = [("heads", C.c_int32), ("vdim", C.c_int32), ("state", C.c_int32), ("groups", C.c_int32), ("conv", C.c_int32),
+                ("norm_groups", C.c_int32)]
 
 
 class LayerDesc(C.Structure):
     """b200_layer_desc"""
     _fields_ = [("mixer", C.c_int32), ("attn", WindowAttnDesc), ("mem", MatrixMemoryDesc), ("attn_scale", C.c_float),
                 ("mem_scale", C.c_float), ("delta", GatedDeltaDesc), ("ff", C.c_int32), ("sattn", SoftmaxAttnDesc),
-                ("ff_kind", C.c_int32), ("moe", MoeDesc)]
+                ("ff_kind", C.c_int32), ("moe", MoeDesc), ("latent", LatentAttnDesc), ("ssd", StateSpaceDesc)]
 
 
 class ProgramDesc(C.Structure):
@@ -130,10 +150,14 @@ class ProgramDesc(C.Structure):
     _fields_ = [("width", C.c_int32), ("vocab", C.c_int32), ("n_layers", C.c_int32), ("max_seq_len", C.c_int32),
                 ("max_batch", C.c_int32), ("norm_eps", C.c_float), ("embed_scale", C.c_float), ("logit_scale", C.c_float),
                 ("pos_sinusoid", C.c_int32), ("loop_start", C.c_int32), ("loop_stop", C.c_int32), ("loop_times", C.c_int32),
-                ("compute", C.c_int32), ("post_norm", C.c_int32), ("residual_alpha", C.c_float), ("norm_weight_offset", C.c_float)]
+                ("compute", C.c_int32), ("post_norm", C.c_int32), ("residual_alpha", C.c_float), ("norm_weight_offset", C.c_float),
+                ("norm_kind", C.c_int32), ("streams", C.c_int32), ("residual_mult", C.c_float)]
 
 
-MIX_WINDOW_MEMORY, MIX_GATED_DELTA, MIX_SOFTMAX_ATTN = 1, 2, 3
+MIX_WINDOW_MEMORY, MIX_GATED_DELTA, MIX_SOFTMAX_ATTN, MIX_LATENT_ATTN, MIX_STATE_SPACE = 1, 2, 3, 4, 5
+NORM_RMS, NORM_LAYER = 0, 1
+ACT_RELU2, ACT_GELU = 0, 1
+ROUTE_TOP_SOFTMAX, ROUTE_SOFTMAX_TOP = 0, 1
 MASK_WINDOW, MASK_CHUNK = 0, 1
 QKNORM_NONE, QKNORM_HEAD_WEIGHT, QKNORM_WHOLE_WEIGHT, QKNORM_HEAD_UNIT = 0, 1, 2, 3
 GATE_NONE, GATE_CHANNEL, GATE_HEAD = 0, 1, 2
@@ -874,7 +898,14 @@ class LayerProgramInference(GpuOnlyInference):
                     for kk, vv in v.items():
                         if kk not in dict(type(sub)._fields_):
                             raise InvalidArgument(f"unknown {k} desc field {kk}")
-                        setattr(sub, kk, vv)
+                        if isinstance(vv, dict):
+                            inner = getattr(sub, kk)
+                            for k3, v3 in vv.items():
+                                if k3 not in dict(type(inner)._fields_):
+                                    raise InvalidArgument(f"unknown {k}.{kk} desc field {k3}")
+                                setattr(inner, k3, v3)
+                        else:
+                            setattr(sub, kk, vv)
                 else:
                     setattr(arr[i], k, v)
         self.program = {k: getattr(pd, k) for k, _ in ProgramDesc._fields_}

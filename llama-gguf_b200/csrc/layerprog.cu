@@ -84,14 +84,30 @@ __global__ void lp_embed_kernel(StepMeta sm, const T* __restrict__ table, const 
 
 // ------------------------------------------------------------------------------------------------ RMS norm
 // out[b] = x[src] / sqrt(mean(x[src]^2) + eps) * w, src = gather ? gather[b] : b.  add != null: x[src] += add first (stored back):
-// the per-pass step vector of a repeated layer range.  One block per row.
+// the per-pass step vector of a repeated layer range.  center = 1: the layer norm, (x - mean) / sqrt(mean((x - mean)^2) + eps) * w
+// (the mean in a pass of its own).  One block per row.
 template <typename OutT>
 __global__ void lp_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ add, const float* __restrict__ w, OutT* __restrict__ out,
-                                  const int* __restrict__ gather, int width, float eps) {
+                                  const int* __restrict__ gather, int width, float eps, int center) {
     const int b = blockIdx.x;
     const int r = gather ? gather[b] : b;
     float* xr = x + (size_t)r * width;
-    __shared__ float red[33];
+    __shared__ float red[34];
+    float mean = 0.0f;
+    if (center) {
+        float t = 0.0f;
+        for (int c = threadIdx.x; c < width; c += blockDim.x) t += xr[c] + (add ? add[c] : 0.0f);
+        t = wsum(t);
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = t;
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            float u = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.0f;
+            u = wsum(u);
+            if (threadIdx.x == 0) red[33] = u / (float)width;
+        }
+        __syncthreads();
+        mean = red[33];
+    }
     float ss = 0.0f;
     for (int c = threadIdx.x; c < width; c += blockDim.x) {
         float v = xr[c];
@@ -99,7 +115,7 @@ __global__ void lp_rmsnorm_kernel(float* __restrict__ x, const float* __restrict
             v += add[c];
             xr[c] = v;
         }
-        ss += v * v;
+        ss += (v - mean) * (v - mean);
     }
     ss = wsum(ss);
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
@@ -111,33 +127,44 @@ __global__ void lp_rmsnorm_kernel(float* __restrict__ x, const float* __restrict
     }
     __syncthreads();
     const float inv = red[32];
-    for (int c = threadIdx.x; c < width; c += blockDim.x) out[(size_t)b * width + c] = from_f<OutT>(xr[c] * inv * w[c]);
+    for (int c = threadIdx.x; c < width; c += blockDim.x) out[(size_t)b * width + c] = from_f<OutT>((xr[c] - mean) * inv * w[c]);
 }
 
 // ------------------------------------------------------------------------------------------------ GEMM (CUDA cores)
 // Y[r][n] = epi(alpha * sum_k X[r][k] * W[n][k]); products of the stored operand values in f32, f32 accumulation.
-enum { EPI_STORE = 0, EPI_ADD = 1, EPI_RELU2 = 2 };
+enum { EPI_STORE = 0, EPI_ADD = 1, EPI_RELU2 = 2, EPI_GELU = 3, EPI_COUNT = 4 };
+__device__ __forceinline__ float gelu_erf_f(float z) { return 0.5f * z * (1.0f + erff(z * 0.7071067811865476f)); }
 template <typename T, int EPI>
 __device__ __forceinline__ void epi_store(void* Y, size_t idx, float v) {
     if (EPI == EPI_STORE) reinterpret_cast<float*>(Y)[idx] = v;
     else if (EPI == EPI_ADD) reinterpret_cast<float*>(Y)[idx] += v;
+    else if (EPI == EPI_GELU) reinterpret_cast<T*>(Y)[idx] = from_f<T>(gelu_erf_f(v));
     else {
         const float z = fmaxf(v, 0.0f);
         reinterpret_cast<T*>(Y)[idx] = from_f<T>(z * z);
     }
 }
 
-// the output row `off` elements on (f32 for the store / add epilogues, the compute type for relu^2)
+// the output row `off` elements on (f32 for the store / add epilogues, the compute type for the activations)
 template <typename T, int EPI>
 __device__ __forceinline__ void* seg_rows(void* Y, size_t off) {
-    return EPI == EPI_RELU2 ? (void*)(reinterpret_cast<T*>(Y) + off) : (void*)(reinterpret_cast<float*>(Y) + off);
+    return (EPI == EPI_RELU2 || EPI == EPI_GELU) ? (void*)(reinterpret_cast<T*>(Y) + off) : (void*)(reinterpret_cast<float*>(Y) + off);
 }
+// Products batched over grid.z without row segments (the heads of a mixer): group z reads X and writes Y `xz` / `yz` elements on
+struct ZStride {
+    size_t x, y;
+};
 constexpr int GB = 64, GK = 16;
 template <typename T, int EPI>
 __global__ void __launch_bounds__(256) lp_gemm_kernel(const T* __restrict__ X, int ldx, const T* __restrict__ W, int ldw, void* __restrict__ Y,
-                                                      int ldy, int R, int N, int K, float alpha, const int* __restrict__ seg, size_t w_zstride) {
+                                                      int ldy, int R, int N, int K, float alpha, const int* __restrict__ seg, size_t w_zstride, ZStride zs) {
     __shared__ float As[GK][GB + 4];
     __shared__ float Bs[GK][GB + 4];
+    if (!seg && gridDim.z > 1) {
+        W += blockIdx.z * w_zstride;
+        X += blockIdx.z * zs.x;
+        Y = seg_rows<T, EPI>(Y, blockIdx.z * zs.y);
+    }
     if (seg) {   // grid.z = group: rows [seg[0], seg[0] + seg[1]) of X and Y, known on the device only (R is the launch's upper bound),
                  // against the group's own weight matrix
         seg += 2 * blockIdx.z;
@@ -226,8 +253,13 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32
 template <int TN, int EPI>
 __global__ void __launch_bounds__(128) lp_gemm_tc_kernel(const bf16* __restrict__ X, int ldx, const bf16* __restrict__ W, int ldw,
                                                          void* __restrict__ Y, int ldy, int R, int N, int K, float alpha, int* err,
-                                                         const int* __restrict__ seg, size_t w_zstride) {
+                                                         const int* __restrict__ seg, size_t w_zstride, ZStride zs) {
     extern __shared__ __align__(1024) uint8_t tc_smem[];
+    if (!seg && gridDim.z > 1) {
+        W += blockIdx.z * w_zstride;
+        X += blockIdx.z * zs.x;
+        Y = seg_rows<bf16, EPI>(Y, blockIdx.z * zs.y);
+    }
     if (seg) {   // grid.z = group: rows [seg[0], seg[0] + seg[1]) of X and Y, known on the device only, against the group's own weight
                  // matrix; a CTA beyond the rows leaves before it holds anything
         seg += 2 * blockIdx.z;
@@ -380,8 +412,11 @@ template <> struct Vec8<float> {
 
 template <typename T, int EPI>
 __global__ void __launch_bounds__(256) lp_gemv_kernel(const T* __restrict__ X, int ldx, const T* __restrict__ W, int ldw, void* __restrict__ Y,
-                                                      int ldy, int R, int N, int K, float alpha, int vec_ok, int stage, RowsTail tail) {
+                                                      int ldy, int R, int N, int K, float alpha, int vec_ok, int stage, RowsTail tail, int nh,
+                                                      ZStride zs) {
+    // nh > 0: the N outputs are heads of nh columns; head z = n / nh reads X `zs.x` elements on and writes column z * zs.y + n % nh
     extern __shared__ __align__(16) uint8_t gv_smem[];
+    const T* X0 = X;
     const int lane = threadIdx.x & 31;
     constexpr int VN = Vec8<T>::N;
     if (stage) {   // the activation rows once per block into shared memory (every warp of the block reads all of them)
@@ -397,6 +432,12 @@ __global__ void __launch_bounds__(256) lp_gemv_kernel(const T* __restrict__ X, i
     }
     for (int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); n < N; n += gridDim.x * (blockDim.x >> 5)) {
     const T* wr = W + (size_t)n * ldw;
+    size_t ycol = n;
+    if (nh > 0) {
+        const int z = n / nh;
+        X = X0 + (size_t)z * zs.x;
+        ycol = (size_t)z * zs.y + (size_t)(n - z * nh);
+    }
     for (int rb = 0; rb < R; rb += GV_ROWS) {
         const int nr = min(GV_ROWS, R - rb);
         float acc[GV_ROWS] = {};
@@ -426,7 +467,7 @@ __global__ void __launch_bounds__(256) lp_gemv_kernel(const T* __restrict__ X, i
         for (int i = 0; i < GV_ROWS; i++) {
             if (i < nr) {
                 const float s = wsum(acc[i]);
-                if (lane == 0) epi_store<T, EPI>(Y, (size_t)(rb + i) * ldy + n, alpha * s);
+                if (lane == 0) epi_store<T, EPI>(Y, (size_t)(rb + i) * ldy + ycol, alpha * s);
             }
         }
     }
@@ -440,16 +481,32 @@ __global__ void __launch_bounds__(256) lp_gemv_kernel(const T* __restrict__ X, i
 template <typename T, int EPI>
 __global__ void __launch_bounds__(256) lp_gemv_norm_kernel(const float* __restrict__ X, const int* __restrict__ gather, const float* __restrict__ nw,
                                                            float eps, const T* __restrict__ W, void* __restrict__ Y, int ldy, int R, int N, int K,
-                                                           float alpha) {
+                                                           float alpha, int center) {
     extern __shared__ __align__(16) uint8_t gn_smem[];
     T* xs = reinterpret_cast<T*>(gn_smem);            // [R][K]
     __shared__ float red[8];
-    __shared__ float inv_s;
+    __shared__ float inv_s, mean_s;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int r = 0; r < R; r++) {
         const float* xr = X + (size_t)(gather ? gather[r] : r) * K;
+        float mean = 0.0f;
+        if (center) {   // layer norm: the mean first
+            float t = 0.0f;
+            for (int k = threadIdx.x; k < K; k += 256) t += xr[k];
+            t = wsum(t);
+            if (lane == 0) red[warp] = t;
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                float u = 0.0f;
+#pragma unroll
+                for (int i = 0; i < 8; i++) u += red[i];
+                mean_s = u / (float)K;
+            }
+            __syncthreads();
+            mean = mean_s;
+        }
         float ss = 0.0f;
-        for (int k = threadIdx.x; k < K; k += 256) ss += xr[k] * xr[k];
+        for (int k = threadIdx.x; k < K; k += 256) ss += (xr[k] - mean) * (xr[k] - mean);
         ss = wsum(ss);
         if (lane == 0) red[warp] = ss;
         __syncthreads();
@@ -461,7 +518,7 @@ __global__ void __launch_bounds__(256) lp_gemv_norm_kernel(const float* __restri
         }
         __syncthreads();
         const float inv = inv_s;
-        for (int k = threadIdx.x; k < K; k += 256) xs[(size_t)r * K + k] = from_f<T>(xr[k] * inv * nw[k]);
+        for (int k = threadIdx.x; k < K; k += 256) xs[(size_t)r * K + k] = from_f<T>((xr[k] - mean) * inv * nw[k]);
     }
     __syncthreads();
     constexpr int VN = Vec8<T>::N;
@@ -510,6 +567,7 @@ struct AttnGeom {
     int chunk;                        // 1: the mask is chunks of `window` positions counted from position 0 instead of a sliding window
     float softcap;                    // > 0: score <- softcap tanh(score / softcap)
     float slope_exp;                  // > 0: score -= 2^(-slope_exp (h + 1) / H) (i - j)
+    int v_in_k;                       // 1: there are no value rows; a value is the first vdim entries of its (single, G = 1) key row
 };
 // out_gate: 0 none, 1 = sigmoid of a gate column per value channel, 2 = one gate column per head
 __device__ __forceinline__ float attn_gate(const AttnGeom& a, const float* gate_row, int h, int ch) {
@@ -566,8 +624,8 @@ __global__ void __launch_bounds__(32 * ATT_WARPS) lp_window_attn_kernel(StepMeta
     const int run = sm.row_run[r], i = sm.row_pos[r];
     const int g = h * a.G / a.H;
     const float* kc = reinterpret_cast<const float*>(sm.run_kv[run] + a.kv_off);
-    const float* vc = kc + (size_t)a.cap * a.G * a.dim;
-    const int ldk = a.G * a.dim, ldv = a.G * a.vdim;
+    const float* vc = a.v_in_k ? kc : kc + (size_t)a.cap * a.G * a.dim;
+    const int ldk = a.G * a.dim, ldv = a.v_in_k ? ldk : a.G * a.vdim;
     if (a.fused_prep) {
         // what lp_attn_prep_kernel does, for this head and its K/V group only: warp 0 norms q into shared memory, warp 1 norms k
         // into the cache row of this position, the other warps copy v there.  Every head of a group writes the same values; a
@@ -741,8 +799,8 @@ __global__ void __launch_bounds__(128) lp_window_attn_tile_kernel(StepMeta sm, A
     if (t0 >= len) return;
     const int g = h * a.G / a.H;
     const float* kc = reinterpret_cast<const float*>(sm.run_kv[run] + a.kv_off);
-    const float* vc = kc + (size_t)a.cap * a.G * a.dim;
-    const int ldk = a.G * a.dim, ldv = a.G * a.vdim;
+    const float* vc = a.v_in_k ? kc : kc + (size_t)a.cap * a.G * a.dim;
+    const int ldk = a.G * a.dim, ldv = a.v_in_k ? ldk : a.G * a.vdim;
     // this thread's two query rows (gid and gid + 8 of the warp's 16) and their positions
     const int tq0 = t0 + warp * 16 + gid, tq1 = tq0 + 8;
     const int i0 = p0 + tq0, i1 = p0 + tq1;
@@ -1044,18 +1102,21 @@ __global__ void __launch_bounds__(SCAN_BD) lp_matrix_memory_kernel(StepMeta sm, 
 // tap meets the current token; inputs before a run's first row come from the run's tail (the last taps - 1 inputs, zero at the
 // start of a sequence).  State block of a run: S [H][dim][vdim] | tail [taps - 1][C], f32.
 struct DeltaGeom {
-    int H, G, dim, vdim, taps, C;     // C = 2 G dim + H vdim
+    int H, G, dim, vdim, taps, C;     // C = 2 G dim + H vdim; the state-space mixer borrows H, dim (= state), vdim, taps, C, in_off, rec_off
     int g_off, b_off, a_off;          // columns of P: gate | write strength | decay
     size_t rec_off;
     float eps;
+    int in_off;                       // first convolved column of P
 };
+// (the convolved channels are columns in_off .. in_off + C of P; bias: one value per channel added to the sum, or null)
 __global__ void lp_conv_silu_kernel(StepMeta sm, DeltaGeom g, const float* __restrict__ P, int ldp, const float* __restrict__ cw,
-                                    float* __restrict__ out, int shift_tail) {
+                                    const float* __restrict__ bias, float* __restrict__ out, int shift_tail) {
     const int r = blockIdx.x, run = sm.row_run[r];
     const int t = r - sm.run_start[run];
     float* tail = reinterpret_cast<float*>(sm.run_rec[run] + g.rec_off) + (size_t)g.H * g.dim * g.vdim;
+    P += g.in_off;
     for (int c = threadIdx.x; c < g.C; c += blockDim.x) {
-        float y = 0.0f;
+        float y = bias ? bias[c] : 0.0f;
         for (int i = 0; i < g.taps; i++) {
             const int tt = t - (g.taps - 1) + i;
             const float in = tt >= 0 ? P[(size_t)(r - t + tt) * ldp + c] : tail[(size_t)(g.taps - 1 + tt) * g.C + c];
@@ -1072,6 +1133,7 @@ __global__ void lp_conv_silu_kernel(StepMeta sm, DeltaGeom g, const float* __res
 __global__ void lp_conv_tail_kernel(StepMeta sm, DeltaGeom g, const float* __restrict__ P, int ldp) {
     const int run = blockIdx.x, r0 = sm.run_start[run], len = sm.run_start[run + 1] - r0;
     float* tail = reinterpret_cast<float*>(sm.run_rec[run] + g.rec_off) + (size_t)g.H * g.dim * g.vdim;
+    P += g.in_off;
     for (int c = threadIdx.x; c < g.C; c += blockDim.x)
         for (int i = 0; i < g.taps - 1; i++) {
             const int st = len + i - (g.taps - 1);
@@ -1229,6 +1291,18 @@ __global__ void lp_argmax_kernel(const float* __restrict__ logits, int vocab, in
 
 #include "lp_softmax_attn.cuh"
 #include "lp_ffn.cuh"
+#include "lp_streams.cuh"
+#include "lp_latent_attn.cuh"
+#include "lp_state_space.cuh"
+
+// out [H][b][a] = in [H][a][b]: a mixer's per-head matrices turned once at load
+template <typename T>
+__global__ void lp_transpose_heads_kernel(const T* __restrict__ in, T* __restrict__ out, int H, int a, int b) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)H * a * b) return;
+    const int h = (int)(i / ((size_t)a * b)), rem = (int)(i - (size_t)h * a * b), ia = rem / b, ib = rem - ia * b;
+    out[(size_t)h * a * b + (size_t)ib * a + ia] = in[i];
+}
 
 __global__ void lp_add_scalar_kernel(float* __restrict__ v, int n, float a) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -1263,6 +1337,17 @@ struct LayerPlan {
     void* wo = nullptr;
     // feed-forward: n_up rows of w_up ([up] | [gate | up] | [router | experts' up | always-on expert's up]), k_down columns of w_down
     int n_up = 0, k_down = 0;
+    // latent attention: W_uq, W_uk turned per head ([H][kv_rank][dim]), W_uv ([H][vdim][kv_rank]); the run whose cache rows it reads
+    LatentGeom lg{};
+    void *w_uq = nullptr, *w_ukT = nullptr, *w_uv = nullptr;
+    const float *dq_norm = nullptr, *dkv_norm = nullptr;
+    float rot_mult = 1.0f;
+    int kv_layer = -1;
+    // state-space mixer
+    SsdGeom sg{};
+    const float *conv_b = nullptr, *ssd_D = nullptr, *ssd_norm = nullptr;
+    // multi-stream layer form: [in | out | mix] of the two sublayers (null: identity)
+    const float *hc_in[2] = {nullptr, nullptr}, *hc_out[2] = {nullptr, nullptr}, *hc_mix[2] = {nullptr, nullptr};
 };
 
 struct SlotMem {
@@ -1294,6 +1379,9 @@ struct LpModel {
     size_t meta_bytes = 0;
     float *x = nullptr, *P = nullptr, *qbuf = nullptr, *O = nullptr, *conv = nullptr, *logits = nullptr;
     float *y = nullptr, *vsrc = nullptr, *moe_w = nullptr, *moe_selw = nullptr;   // sublayer output (norm-after-sum layers), shared values, routing
+    float* xs = nullptr;                // [rows][streams][width]: the residual copies of the multi-stream layer form
+    void* cq = nullptr;                 // [rows][max_qrank] compute type: the normed query latent
+    int max_qrank = 0;
     int *moe_sel = nullptr, *moe_pos = nullptr, *moe_seg = nullptr;   // chosen experts per row; row of (token, choice) in expert order; {first, rows} per expert
     void* moe_xp = nullptr;             // the tokens' rows gathered in expert order, compute type
     float* moe_yp = nullptr;            // the experts' outputs in the same order
@@ -1379,7 +1467,8 @@ bool is_matrix_name(const std::string& n) {
     // everything a GEMM or the embedding gather reads; the rest (norm weights, biases, convolution taps, per-head constants, step
     // vectors) is kept in f32
     if (n == "embed" || n == "head") return true;
-    static const char* suf[] = {".q", ".k", ".v", ".g", ".o", ".i", ".f", ".a", ".b", ".up", ".down", ".gate", ".router"};
+    static const char* suf[] = {".q", ".k", ".v", ".g", ".o", ".i", ".f", ".a", ".b", ".up", ".down", ".gate", ".router",
+                                ".dq", ".uq", ".dkv", ".uk", ".uv", ".in"};
     for (const char* s : suf) {
         const size_t L = strlen(s);
         if (n.size() > L && n.compare(n.size() - L, L, s) == 0) return true;
@@ -1401,9 +1490,9 @@ void launch(LpModel* m, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t sm
 // The tensor-core GEMM takes bf16 operands whose rows are 16-byte aligned (K and the row pitches multiples of 8).
 template <int TN>
 bool tc_launch(LpModel* m, const bf16* x, int ldx, const bf16* w, int ldw, int N, int K, void* Y, int ldy, int R, float alpha, int epi, const int* seg,
-               int groups, size_t zs) {
+               int groups, size_t wz, ZStride zs) {
     const size_t smem = (size_t)TC_STAGES * (TC_M + TN) * 128 + 1024;
-    static bool once[3][64] = {};
+    static bool once[EPI_COUNT][64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     auto prep = [&](auto kern, int e) {
@@ -1416,53 +1505,65 @@ bool tc_launch(LpModel* m, const bf16* x, int ldx, const bf16* w, int ldw, int N
         return true;
     };
     dim3 grid((N + TC_M - 1) / TC_M, (R + TN - 1) / TN, groups), block(128);
-    if (epi == EPI_STORE) {
-        if (!prep(lp_gemm_tc_kernel<TN, EPI_STORE>, 0)) return false;
-        launch(m, lp_gemm_tc_kernel<TN, EPI_STORE>, grid, block, smem, x, ldx, w, ldw, Y, ldy, R, N, K, alpha, m->tc_err, seg, zs);
-    } else if (epi == EPI_ADD) {
-        if (!prep(lp_gemm_tc_kernel<TN, EPI_ADD>, 1)) return false;
-        launch(m, lp_gemm_tc_kernel<TN, EPI_ADD>, grid, block, smem, x, ldx, w, ldw, Y, ldy, R, N, K, alpha, m->tc_err, seg, zs);
-    } else {
-        if (!prep(lp_gemm_tc_kernel<TN, EPI_RELU2>, 2)) return false;
-        launch(m, lp_gemm_tc_kernel<TN, EPI_RELU2>, grid, block, smem, x, ldx, w, ldw, Y, ldy, R, N, K, alpha, m->tc_err, seg, zs);
-    }
+#define LP_TC(E)                                                                                                                       \
+    do {                                                                                                                               \
+        if (!prep(lp_gemm_tc_kernel<TN, E>, E)) return false;                                                                          \
+        launch(m, lp_gemm_tc_kernel<TN, E>, grid, block, smem, x, ldx, w, ldw, Y, ldy, R, N, K, alpha, m->tc_err, seg, wz, zs);        \
+    } while (0)
+    if (epi == EPI_STORE) LP_TC(EPI_STORE);
+    else if (epi == EPI_ADD) LP_TC(EPI_ADD);
+    else if (epi == EPI_GELU) LP_TC(EPI_GELU);
+    else LP_TC(EPI_RELU2);
+#undef LP_TC
     return true;
 }
 bool tc_gemm(LpModel* m, const void* X, int ldx, const void* W, int ldw, int N, int K, void* Y, int ldy, int R, float alpha, int epi, const int* seg,
-             int groups, size_t zs) {
+             int groups, size_t wz, ZStride zs) {
     if (m->f32 || !m->use_tc || R < m->tc_min_rows) return false;
-    if (K % 8 || ldx % 8 || ldw % 8 || zs % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return false;
+    if (K % 8 || ldx % 8 || ldw % 8 || wz % 8 || zs.x % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return false;
     const bf16* x = (const bf16*)X;
     const bf16* w = (const bf16*)W;
-    if (R <= 64) return tc_launch<64>(m, x, ldx, w, ldw, N, K, Y, ldy, R, alpha, epi, seg, groups, zs);
-    if (R <= 128) return tc_launch<128>(m, x, ldx, w, ldw, N, K, Y, ldy, R, alpha, epi, seg, groups, zs);   // (wider token tiles move fewer operand bytes per FLOP: measured 2.5x on a 2048 x 8192 x 2048 product even at 128 CTAs)
-    return tc_launch<256>(m, x, ldx, w, ldw, N, K, Y, ldy, R, alpha, epi, seg, groups, zs);
+    if (R <= 64) return tc_launch<64>(m, x, ldx, w, ldw, N, K, Y, ldy, R, alpha, epi, seg, groups, wz, zs);
+    if (R <= 128) return tc_launch<128>(m, x, ldx, w, ldw, N, K, Y, ldy, R, alpha, epi, seg, groups, wz, zs);   // (wider token tiles move fewer operand bytes per FLOP: measured 2.5x on a 2048 x 8192 x 2048 product even at 128 CTAs)
+    return tc_launch<256>(m, x, ldx, w, ldw, N, K, Y, ldy, R, alpha, epi, seg, groups, wz, zs);
 }
 
-// Y = epi(alpha X W^T): rows of the step against a [N][K] matrix in the compute type
+// Y = epi(alpha X W^T): rows of the step against a [N][K] matrix in the compute type.  Without `seg`, groups > 1 batches the product
+// over heads: head z multiplies columns [z zs.x, z zs.x + K) of X with rows [z N, (z + 1) N) of W (wz = N ldw) into columns
+// [z zs.y, z zs.y + N) of Y.
 template <typename T>
 void gemm_t(LpModel* m, const void* X, int ldx, const void* W, int ldw, int N, int K, void* Y, int ldy, int R, float alpha, int epi, const int* seg = nullptr,
-            int groups = 1, size_t zs = 0, const RowsTail* tail = nullptr) {
+            int groups = 1, size_t wz = 0, const RowsTail* tail = nullptr, ZStride zs = ZStride{0, 0}) {
     const T* x = (const T*)X;
     const T* w = (const T*)W;
     if (R <= 2 * GV_ROWS && !seg) {
         constexpr int VN = Vec8<T>::N;
-        const int vec_ok = (K % VN == 0 && ldx % VN == 0 && ldw % VN == 0 && ((uintptr_t)X % 16) == 0 && ((uintptr_t)W % 16) == 0) ? 1 : 0;
+        const bool heads = groups > 1;
+        const int vec_ok = (K % VN == 0 && ldx % VN == 0 && ldw % VN == 0 && zs.x % VN == 0 && ((uintptr_t)X % 16) == 0 && ((uintptr_t)W % 16) == 0) ? 1 : 0;
         // a few blocks per SM, each walking its share of the output columns with the activation rows staged once
-        dim3 grid(std::min((N + 7) / 8, 4 * 148)), block(256);
+        const int Nall = N * groups;
+        dim3 grid(std::min((Nall + 7) / 8, 4 * 148)), block(256);
         const size_t xbytes = (size_t)R * K * sizeof(T);
-        const int stage = (vec_ok && sizeof(T) * VN == 16 && xbytes <= 48 * 1024) ? 1 : 0;
+        const int stage = (!heads && vec_ok && sizeof(T) * VN == 16 && xbytes <= 48 * 1024) ? 1 : 0;
         const size_t smem = stage ? xbytes : 0;
-        if (epi == EPI_STORE) launch(m, lp_gemv_kernel<T, EPI_STORE>, grid, block, smem, x, ldx, w, ldw, Y, ldy, R, N, K, alpha, vec_ok, stage, tail ? *tail : RowsTail{});
-        else if (epi == EPI_ADD) launch(m, lp_gemv_kernel<T, EPI_ADD>, grid, block, smem, x, ldx, w, ldw, Y, ldy, R, N, K, alpha, vec_ok, stage, tail ? *tail : RowsTail{});
-        else launch(m, lp_gemv_kernel<T, EPI_RELU2>, grid, block, smem, x, ldx, w, ldw, Y, ldy, R, N, K, alpha, vec_ok, stage, tail ? *tail : RowsTail{});
+        const RowsTail tl = tail ? *tail : RowsTail{};
+        const int nh = heads ? N : 0;
+#define LP_GV(E) launch(m, lp_gemv_kernel<T, E>, grid, block, smem, x, ldx, w, ldw, Y, ldy, R, Nall, K, alpha, vec_ok, stage, tl, nh, zs)
+        if (epi == EPI_STORE) LP_GV(EPI_STORE);
+        else if (epi == EPI_ADD) LP_GV(EPI_ADD);
+        else if (epi == EPI_GELU) LP_GV(EPI_GELU);
+        else LP_GV(EPI_RELU2);
+#undef LP_GV
         return;
     }
-    if (tc_gemm(m, X, ldx, W, ldw, N, K, Y, ldy, R, alpha, epi, seg, groups, zs)) return;
+    if (tc_gemm(m, X, ldx, W, ldw, N, K, Y, ldy, R, alpha, epi, seg, groups, wz, zs)) return;
     dim3 grid((N + GB - 1) / GB, (R + GB - 1) / GB, groups), block(256);
-    if (epi == EPI_STORE) launch(m, lp_gemm_kernel<T, EPI_STORE>, grid, block, 0, x, ldx, w, ldw, Y, ldy, R, N, K, alpha, seg, zs);
-    else if (epi == EPI_ADD) launch(m, lp_gemm_kernel<T, EPI_ADD>, grid, block, 0, x, ldx, w, ldw, Y, ldy, R, N, K, alpha, seg, zs);
-    else launch(m, lp_gemm_kernel<T, EPI_RELU2>, grid, block, 0, x, ldx, w, ldw, Y, ldy, R, N, K, alpha, seg, zs);
+#define LP_GM(E) launch(m, lp_gemm_kernel<T, E>, grid, block, 0, x, ldx, w, ldw, Y, ldy, R, N, K, alpha, seg, wz, zs)
+    if (epi == EPI_STORE) LP_GM(EPI_STORE);
+    else if (epi == EPI_ADD) LP_GM(EPI_ADD);
+    else if (epi == EPI_GELU) LP_GM(EPI_GELU);
+    else LP_GM(EPI_RELU2);
+#undef LP_GM
 }
 // tail: few rows only (the caller has checked R): the last block goes on with rows_tail
 void gemm(LpModel* m, const void* X, int ldx, const void* W, int N, int K, void* Y, int ldy, int R, float alpha, int epi, const RowsTail* tail = nullptr) {
@@ -1477,15 +1578,22 @@ void gemm_grouped(LpModel* m, const void* X, int ldx, const void* Wm, int ldw, s
     if (m->f32) gemm_t<float>(m, X, ldx, Wm, ldw, N, K, Y, ldy, R, 1.0f, epi, seg, groups, zs);
     else gemm_t<bf16>(m, X, ldx, Wm, ldw, N, K, Y, ldy, R, 1.0f, epi, seg, groups, zs);
 }
+// One product per head in one launch: Y[r][z yz + n] = sum_k X[r][z xz + k] Wm[z N + n][k], z < heads, all rows of the step (f32 out).
+void gemm_heads(LpModel* m, const void* X, int ldx, size_t xz, const void* Wm, int heads, int N, int K, void* Y, int ldy, size_t yz, int R) {
+    if (m->f32) gemm_t<float>(m, X, ldx, Wm, K, N, K, Y, ldy, R, 1.0f, EPI_STORE, nullptr, heads, (size_t)N * K, nullptr, ZStride{xz, yz});
+    else gemm_t<bf16>(m, X, ldx, Wm, K, N, K, Y, ldy, R, 1.0f, EPI_STORE, nullptr, heads, (size_t)N * K, nullptr, ZStride{xz, yz});
+}
 // One product with a weight matrix whose rows are `ldw` apart (a block of columns of a wider matrix).
 void gemm_ld(LpModel* m, const void* X, int ldx, const void* Wm, int ldw, int N, int K, void* Y, int ldy, int R, int epi) {
     if (m->f32) gemm_t<float>(m, X, ldx, Wm, ldw, N, K, Y, ldy, R, 1.0f, epi);
     else gemm_t<bf16>(m, X, ldx, Wm, ldw, N, K, Y, ldy, R, 1.0f, epi);
 }
 
+int norm_center(const LpModel* m) { return m->p.norm_kind == B200_NORM_LAYER ? 1 : 0; }
+
 void rmsnorm(LpModel* m, float* x, const float* add, const float* w, void* out, const int* gather, int rows) {
-    if (m->f32) launch(m, lp_rmsnorm_kernel<float>, dim3(rows), dim3(128), 0, x, add, w, (float*)out, gather, m->p.width, m->p.norm_eps);
-    else launch(m, lp_rmsnorm_kernel<bf16>, dim3(rows), dim3(128), 0, x, add, w, (bf16*)out, gather, m->p.width, m->p.norm_eps);
+    if (m->f32) launch(m, lp_rmsnorm_kernel<float>, dim3(rows), dim3(128), 0, x, add, w, (float*)out, gather, m->p.width, m->p.norm_eps, norm_center(m));
+    else launch(m, lp_rmsnorm_kernel<bf16>, dim3(rows), dim3(128), 0, x, add, w, (bf16*)out, gather, m->p.width, m->p.norm_eps, norm_center(m));
 }
 
 // norm + projection of the step's rows: one fused kernel for a few rows (decoding) when the normed rows fit in shared memory,
@@ -1497,7 +1605,7 @@ bool gemv_norm_t(LpModel* m, const float* x, const int* gather, const float* nw,
     constexpr int VN = Vec8<T>::N;
     const size_t smem = (size_t)R * K * sizeof(T);
     if (R > 2 * GV_ROWS || K % VN || ((uintptr_t)W & 15) || smem > 96 * 1024) return false;
-    static bool once[3][64] = {};
+    static bool once[EPI_COUNT][64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     auto prep = [&](auto kern, int e) {
@@ -1513,10 +1621,10 @@ bool gemv_norm_t(LpModel* m, const float* x, const int* gather, const float* nw,
     const T* w = (const T*)W;
     if (epi == EPI_STORE) {
         if (!prep(lp_gemv_norm_kernel<T, EPI_STORE>, 0)) return false;
-        launch(m, lp_gemv_norm_kernel<T, EPI_STORE>, grid, block, smem, x, gather, nw, m->p.norm_eps, w, Y, ldy, R, N, K, alpha);
+        launch(m, lp_gemv_norm_kernel<T, EPI_STORE>, grid, block, smem, x, gather, nw, m->p.norm_eps, w, Y, ldy, R, N, K, alpha, norm_center(m));
     } else if (epi == EPI_RELU2) {
         if (!prep(lp_gemv_norm_kernel<T, EPI_RELU2>, 2)) return false;
-        launch(m, lp_gemv_norm_kernel<T, EPI_RELU2>, grid, block, smem, x, gather, nw, m->p.norm_eps, w, Y, ldy, R, N, K, alpha);
+        launch(m, lp_gemv_norm_kernel<T, EPI_RELU2>, grid, block, smem, x, gather, nw, m->p.norm_eps, w, Y, ldy, R, N, K, alpha, norm_center(m));
     } else return false;
     return true;
 }
@@ -1545,6 +1653,10 @@ int lp_create(const b200_program_desc* prog, const b200_layer_desc* layers, int 
     if (p.compute != B200_COMPUTE_BF16 && p.compute != B200_COMPUTE_F32) return bad("compute must be B200_COMPUTE_BF16 or B200_COMPUTE_F32");
     const bool looped = p.loop_stop > p.loop_start;
     if (looped && (p.loop_start < 0 || p.loop_stop > p.n_layers || p.loop_times < 1)) return bad("bad repeated layer range");
+    if (p.norm_kind != B200_NORM_RMS && p.norm_kind != B200_NORM_LAYER) return bad("unknown norm kind");
+    if (p.norm_kind == B200_NORM_LAYER && p.post_norm) return bad("the layer norm is not available in the norm-after-sum form");
+    if (p.streams < 0 || p.streams > ST_MAX) return bad("streams must be 0 .. " + std::to_string(ST_MAX));
+    if (p.streams > 0 && (p.post_norm || looped)) return bad("the multi-stream form takes neither the norm after the sum nor a repeated range");
     for (int i = 0; i < p.n_layers; i++) {
         const b200_layer_desc& L = layers[i];
         const std::string at = "layer " + std::to_string(i) + ": ";
@@ -1579,10 +1691,33 @@ int lp_create(const b200_program_desc* prog, const b200_layer_desc* layers, int 
                 if (layers[src].sattn.kv_heads * layers[src].sattn.vdim != a.kv_heads * a.vdim) return bad(at + "blended values differ in size from their source");
             }
             if (looped && a.v_mix != B200_VMIX_NONE) return bad(at + "value mixing inside a program with a repeated range is not supported");
+        } else if (L.mixer == B200_MIX_LATENT_ATTN) {
+            const b200_latent_attn_desc& a = L.latent;
+            if (a.heads <= 0 || a.dim <= 0 || a.rot_dim < 0 || a.vdim <= 0 || a.q_rank <= 0 || a.kv_rank <= 0) return bad(at + "bad latent-attention sizes");
+            if (a.kv_rank > 32 * ATT_ACC) return bad(at + "latent size above " + std::to_string(32 * ATT_ACC));
+            if (a.mask_size < 0) return bad(at + "negative window");
+            if (a.rot.dims < 0 || a.rot.dims > a.rot_dim || (a.rot.dims & 1) || (a.rot.dims > 0 && !(a.rot.base > 0.0f))) return bad(at + "bad rotary sizes");
+            if (a.rot.yarn_factor < 0.0f || (a.rot.yarn_factor > 0.0f && !(a.rot.yarn_original > 0.0f && a.rot.yarn_fast > 0.0f && a.rot.yarn_slow > 0.0f)))
+                return bad(at + "bad rotary scaling");
+            if (a.out_gate != B200_GATE_NONE && a.out_gate != B200_GATE_CHANNEL) return bad(at + "latent attention takes no gate or one per value channel");
+            if (a.kv_from >= 0) {
+                if (a.kv_from >= i || layers[a.kv_from].mixer != B200_MIX_LATENT_ATTN || layers[a.kv_from].latent.kv_from >= 0)
+                    return bad(at + "kv_from must name an earlier latent-attention layer with cache rows of its own");
+                const b200_latent_attn_desc& o = layers[a.kv_from].latent;
+                if (o.kv_rank != a.kv_rank || o.rot_dim != a.rot_dim) return bad(at + "borrowed cache rows differ in size");
+                if (looped) return bad(at + "borrowed cache rows inside a program with a repeated range are not supported");
+            }
+        } else if (L.mixer == B200_MIX_STATE_SPACE) {
+            const b200_state_space_desc& g = L.ssd;
+            if (g.heads <= 0 || g.vdim <= 0 || g.state <= 0 || g.groups <= 0 || g.conv < 1 || g.norm_groups <= 0) return bad(at + "bad state-space sizes");
+            if (g.heads % g.groups || (g.heads * g.vdim) % g.norm_groups) return bad(at + "state-space heads / groups do not divide");
+            if (g.state > 256) return bad(at + "state size above 256");
         } else return bad(at + "unknown mixer");
         if (L.ff_kind == B200_FF_MOE) {
             const b200_moe_desc& e = L.moe;
             if (e.experts <= 0 || e.top <= 0 || e.top > e.experts || e.expert_ff <= 0 || e.shared_ff < 0) return bad(at + "bad mixture-of-experts sizes");
+            if ((e.act != B200_ACT_RELU2 && e.act != B200_ACT_GELU) || (e.route != B200_ROUTE_TOP_SOFTMAX && e.route != B200_ROUTE_SOFTMAX_TOP))
+                return bad(at + "unknown expert activation or routing rule");
         } else if (L.ff_kind != B200_FF_RELU2 && L.ff_kind != B200_FF_GATED_GELU) return bad(at + "unknown feed-forward kind");
         if (L.ff < 0) return bad(at + "negative feed-forward width");
     }
@@ -1844,6 +1979,95 @@ int lp_finalize(LpModel* m, std::string* err) {
             m->max_act = std::max(m->max_act, a.heads * a.vdim);
             m->max_q = std::max(m->max_q, (int)nq);
             if (a.v_mix != B200_VMIX_NONE) m->max_vsrc = std::max(m->max_vsrc, (int)nv);
+        } else if (L.d.mixer == B200_MIX_LATENT_ATTN) {
+            const b200_latent_attn_desc& a = L.d.latent;
+            const std::string x = pre + "mix.";
+            const bool own = a.kv_from < 0;
+            const uint64_t H = a.heads, D = (uint64_t)a.kv_rank + a.rot_dim, per = (uint64_t)a.dim + a.rot_dim;
+            std::vector<std::string> names = {x + "dq"};
+            std::vector<uint64_t> rows = {(uint64_t)a.q_rank};
+            if (own) { names.push_back(x + "dkv"); rows.push_back(D); }
+            if (a.out_gate) { names.push_back(x + "g"); rows.push_back(H * a.vdim); }
+            if ((rc = fuse_rows(m, names, rows, W, &L.w_in, &L.n_in, &off, err))) return rc;
+            LatentGeom& g = L.lg;
+            g.H = a.heads; g.dim = a.dim; g.rot_dim = a.rot_dim; g.vdim = a.vdim; g.q_rank = a.q_rank; g.kv_rank = a.kv_rank;
+            g.rot_n = a.rot.dims; g.eps = p.norm_eps; g.cap = p.max_seq_len;
+            g.q_off = off[0]; g.kv_off = own ? off[1] : -1; g.g_off = a.out_gate ? off[own ? 2 : 1] : 0;
+            if ((rc = need_vec(m, x + "dq.norm", a.q_rank, &L.dq_norm, err))) return rc;
+            if (own && (rc = need_vec(m, x + "dkv.norm", a.kv_rank, &L.dkv_norm, err))) return rc;
+            if ((rc = need_mat(m, x + "uq", H * per, a.q_rank, &L.w_uq, err))) return rc;
+            if ((rc = need_mat(m, x + "uv", H * a.vdim, a.kv_rank, &L.w_uv, err))) return rc;
+            if ((rc = need_mat(m, x + "o", W, H * a.vdim, &L.wo, err))) return rc;
+            {   // W_uk [H dim][kv_rank] -> per head [kv_rank][dim]: the matrix that carries a head's plain query into the latent
+                void* uk;
+                if ((rc = need_mat(m, x + "uk", H * a.dim, a.kv_rank, &uk, err))) return rc;
+                Tensor t = *find(m, x + "uk");
+                LCU_ALLOC(cudaMalloc(&t.d, up16(t.bytes)));
+                const size_t n = (size_t)H * a.dim * a.kv_rank;
+                if (m->f32) lp_transpose_heads_kernel<float><<<(unsigned)((n + 255) / 256), 256>>>((const float*)uk, (float*)t.d, a.heads, a.dim, a.kv_rank);
+                else lp_transpose_heads_kernel<bf16><<<(unsigned)((n + 255) / 256), 256>>>((const bf16*)uk, (bf16*)t.d, a.heads, a.dim, a.kv_rank);
+                LCU(cudaDeviceSynchronize());
+                cudaFree(uk);
+                m->tensors.erase(x + "uk");
+                t.rows = H * a.kv_rank; t.cols = a.dim;
+                m->tensors[x + "uk.t"] = t;
+                L.w_ukT = t.d;
+            }
+            if (a.rot.dims > 0) {   // frequencies of the pairs, in double (see b200_rotary_desc)
+                const b200_rotary_desc& ro = a.rot;
+                const int half = ro.dims / 2;
+                std::vector<double> f(half);
+                for (int i = 0; i < half; i++) f[i] = std::pow((double)ro.base, -2.0 * (double)i / (double)ro.dims);
+                g.rot_mult = 1.0f;
+                if (ro.yarn_factor > 0.0f) {
+                    const double pi = 3.14159265358979323846;
+                    auto turn_dim = [&](double t) { return (double)ro.dims * std::log((double)ro.yarn_original / (2.0 * pi * t)) / (2.0 * std::log((double)ro.base)); };
+                    const double lo = std::max(std::floor(turn_dim(ro.yarn_fast)), 0.0), hi = std::min(std::ceil(turn_dim(ro.yarn_slow)), (double)ro.dims - 1.0);
+                    for (int i = 0; i < half; i++) {
+                        const double ramp = std::min(1.0, std::max(0.0, ((double)i - lo) / std::max(hi - lo, 0.001)));
+                        f[i] = f[i] / (double)ro.yarn_factor * ramp + f[i] * (1.0 - ramp);
+                    }
+                    g.rot_mult = (float)(0.1 * std::log((double)ro.yarn_factor) + 1.0);
+                }
+                double* d = nullptr;
+                LCU_ALLOC(cudaMalloc((void**)&d, up16(f.size() * 8)));
+                LCU(cudaMemcpy(d, f.data(), f.size() * 8, cudaMemcpyHostToDevice));
+                Tensor t;
+                t.d = d; t.rows = 1; t.cols = f.size(); t.bytes = f.size() * 8;
+                m->tensors[x + "rot.freq"] = t;
+                L.rot_freq = d;
+            }
+            AttnGeom& ag = L.ag;   // the cached rows as one K/V head: keys = the whole row, values = its first kv_rank entries
+            ag.H = a.heads; ag.G = 1; ag.dim = (int)D; ag.vdim = a.kv_rank; ag.window = a.mask_size > 0 ? a.mask_size : p.max_seq_len;
+            ag.scale = a.scale; ag.eps = p.norm_eps; ag.cap = p.max_seq_len; ag.v_in_k = 1;
+            L.kv_bytes = own ? up16((size_t)p.max_seq_len * D * 4) : 0;
+            L.kv_layer = own ? li : a.kv_from;
+            m->max_act = std::max(m->max_act, (int)(H * std::max(std::max(a.dim, a.kv_rank), a.vdim)));
+            m->max_q = std::max(m->max_q, (int)(H * D));
+            m->max_o = std::max(m->max_o, (int)(H * std::max(per, (uint64_t)a.vdim)));
+            m->max_qrank = std::max(m->max_qrank, a.q_rank);
+        } else if (L.d.mixer == B200_MIX_STATE_SPACE) {
+            const b200_state_space_desc& g = L.d.ssd;
+            const std::string x = pre + "mix.";
+            const uint64_t inner = (uint64_t)g.heads * g.vdim, gn = (uint64_t)g.groups * g.state, C = inner + 2 * gn;
+            L.n_in = (int)(2 * inner + 2 * gn + g.heads);
+            if ((rc = need_mat(m, x + "in", L.n_in, W, &L.w_in, err))) return rc;
+            m->tensors.erase(x + "in");   // (the plan owns its input projection)
+            DeltaGeom& d = L.dg;          // the convolution's view: C channels from column `inner` on, the tail behind the matrix states
+            d.H = g.heads; d.dim = g.state; d.vdim = g.vdim; d.taps = g.conv; d.C = (int)C; d.in_off = (int)inner;
+            SsdGeom& q = L.sg;
+            q.H = g.heads; q.G = g.groups; q.N = g.state; q.vdim = g.vdim; q.dt_off = (int)(inner + C);
+            if ((rc = need_vec(m, x + "conv", C * g.conv, &L.conv_w, err))) return rc;
+            if ((rc = need_vec(m, x + "conv.b", C, &L.conv_b, err))) return rc;
+            if ((rc = need_vec(m, x + "A_log", g.heads, &L.A_log, err))) return rc;
+            if ((rc = need_vec(m, x + "dt_bias", g.heads, &L.dt_bias, err))) return rc;
+            if ((rc = need_vec(m, x + "D", g.heads, &L.ssd_D, err))) return rc;
+            if ((rc = need_vec(m, x + "norm", inner, &L.ssd_norm, err))) return rc;
+            if ((rc = need_mat(m, x + "o", W, inner, &L.wo, err))) return rc;
+            L.rec_bytes = up16(((size_t)g.heads * g.state * g.vdim + (size_t)(g.conv - 1) * C) * 4);
+            m->max_act = std::max(m->max_act, (int)inner);
+            m->max_o = std::max(m->max_o, (int)inner);
+            m->max_conv = std::max(m->max_conv, (int)C);
         } else {
             const b200_gated_delta_desc& g = L.d.delta;
             const std::string x = pre + "mix.";
@@ -1878,6 +2102,15 @@ int lp_finalize(LpModel* m, std::string* err) {
             m->max_conv = std::max(m->max_conv, d.C);
         }
         m->max_in = std::max(m->max_in, L.n_in);
+        if (p.streams > 0) {   // the stream weights of the two sublayers; a layer without them mixes nothing
+            for (int q = 0; q < 2; q++) {
+                const std::string hc = pre + "hc" + std::to_string(q + 1) + ".";
+                if (!find(m, hc + "in")) continue;
+                if ((rc = need_vec(m, hc + "in", p.streams, &L.hc_in[q], err))) return rc;
+                if ((rc = need_vec(m, hc + "out", p.streams, &L.hc_out[q], err))) return rc;
+                if ((rc = need_vec(m, hc + "mix", (uint64_t)p.streams * p.streams, &L.hc_mix[q], err))) return rc;
+            }
+        }
         if (L.d.ff_kind == B200_FF_MOE) {
             const b200_moe_desc& e = L.d.moe;
             if ((rc = need_vec(m, pre + "norm2", W, &L.norm2, err))) return rc;
@@ -1968,6 +2201,7 @@ int lp_finalize(LpModel* m, std::string* err) {
         m->weight_bytes += 0;
         if (L.d.mixer == B200_MIX_WINDOW_MEMORY) m->kv_bytes_per_pos += (size_t)L.d.attn.kv_heads * (L.d.attn.dim + L.d.attn.vdim) * 4;
         if (L.d.mixer == B200_MIX_SOFTMAX_ATTN) m->kv_bytes_per_pos += (size_t)L.d.sattn.kv_heads * (L.d.sattn.dim + L.d.sattn.vdim) * 4;
+        if (L.d.mixer == B200_MIX_LATENT_ATTN && L.d.latent.kv_from < 0) m->kv_bytes_per_pos += (size_t)(L.d.latent.kv_rank + L.d.latent.rot_dim) * 4;
     }
     m->slot_kv_bytes = std::max<size_t>(kv, 256);
     m->slot_rec_bytes = std::max<size_t>(rec, 256);
@@ -1978,6 +2212,13 @@ int lp_finalize(LpModel* m, std::string* err) {
         for (int i = 0; i < nf; i++) f[i] = std::pow(10000.0, -2.0 * (double)i / (double)p.width);
         LCU_ALLOC(cudaMalloc((void**)&m->inv_freq, up16(nf * sizeof(double))));
         LCU(cudaMemcpy(m->inv_freq, f.data(), nf * sizeof(double), cudaMemcpyHostToDevice));
+    }
+    if (p.streams > 0) {   // the stream kernel keeps a row of the width in shared memory
+        if ((size_t)p.width * 4 > 200 * 1024) return lp_fail(err, B200_ERR_UNSUPPORTED, "multi-stream form: a row exceeds 200 KB of shared memory");
+        if ((size_t)p.width * 4 > 48 * 1024) {
+            LCU(cudaFuncSetAttribute(lp_streams_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, p.width * 4));
+            LCU(cudaFuncSetAttribute(lp_streams_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, p.width * 4));
+        }
     }
     LCU_ALLOC(cudaMalloc((void**)&m->tc_err, 256));
     LCU(cudaMemset(m->tc_err, 0, 256));
@@ -2003,7 +2244,7 @@ void lp_destroy(LpModel* m) {
     for (SlotMem& s : m->pool) { cudaFree(s.kv); cudaFree(s.rec); }
     for (void* ptr : {(void*)m->inv_freq, (void*)m->d_meta, (void*)m->x, (void*)m->P, (void*)m->qbuf, (void*)m->O, (void*)m->conv, (void*)m->logits,
                       m->hn, m->act_a, m->hw, (void*)m->pick, (void*)m->taps, (void*)m->y, (void*)m->vsrc, (void*)m->moe_w, (void*)m->moe_selw,
-                      (void*)m->moe_sel, (void*)m->moe_pos, (void*)m->moe_seg, m->moe_xp, (void*)m->moe_yp})
+                      (void*)m->moe_sel, (void*)m->moe_pos, (void*)m->moe_seg, m->moe_xp, (void*)m->moe_yp, (void*)m->xs, m->cq})
         cudaFree(ptr);
     if (m->h_meta) cudaFreeHost(m->h_meta);
     if (m->h_logits) cudaFreeHost(m->h_logits);
@@ -2065,11 +2306,13 @@ int ensure_scratch(LpModel* m, int R, int n_runs, int n_want, std::string* err) 
         if ((rc = grow(&m->x, (size_t)cap * W * 4, err))) return rc;
         if ((rc = grow(&m->P, (size_t)cap * m->max_in * 4, err))) return rc;
         if ((rc = grow(&m->qbuf, (size_t)cap * std::max(m->max_q, 1) * 4, err))) return rc;
-        if ((rc = grow(&m->O, (size_t)cap * m->max_o * 4, err))) return rc;
+        if ((rc = grow(&m->O, (size_t)cap * std::max(m->max_o, 1) * 4, err))) return rc;
         if ((rc = grow(&m->conv, (size_t)cap * std::max(m->max_conv, 1) * 4, err))) return rc;
         if ((rc = grow(&m->hn, (size_t)cap * W * es, err))) return rc;
         if ((rc = grow(&m->act_a, (size_t)cap * m->max_act * es, err))) return rc;
-        if ((m->p.post_norm || m->max_experts > 0) && (rc = grow(&m->y, (size_t)cap * W * 4, err))) return rc;
+        if ((m->p.post_norm || m->max_experts > 0 || m->p.streams > 0) && (rc = grow(&m->y, (size_t)cap * W * 4, err))) return rc;
+        if (m->p.streams > 0 && (rc = grow(&m->xs, (size_t)cap * m->p.streams * W * 4, err))) return rc;
+        if (m->max_qrank > 0 && (rc = grow(&m->cq, (size_t)cap * m->max_qrank * es, err))) return rc;
         if (m->max_vsrc > 0 && (rc = grow(&m->vsrc, (size_t)cap * m->max_vsrc * 4, err))) return rc;
         if (m->max_experts > 0) {
             if ((rc = grow(&m->moe_w, (size_t)cap * m->max_experts * 4, err))) return rc;
@@ -2154,13 +2397,32 @@ void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want,
     // The two layer forms.  Norm first: a sublayer reads norm(x) and its output projection adds into x.  Norm after the sum
     // (post_norm): a sublayer reads x itself -- m->hn holds x in the compute type -- its output projection goes to m->y, and
     // lp_postnorm_kernel makes x <- norm(alpha x + y) and the next copy.
-    const bool post = p.post_norm != 0;
+    // Multi-stream form (p.streams >= 1): the copies live in m->xs; a sublayer's output goes to m->y and waits in `pend` until the
+    // next sublayer (or the head) asks for its input: lp_streams_kernel then updates the copies and norms their weighted sum into m->hn.
+    const bool post = p.post_norm != 0, streams = p.streams > 0;
+    struct {
+        const float *y, *mix, *out;
+        bool src;
+    } pend = {nullptr, nullptr, nullptr, true};
+    auto boundary = [&](const float* in, const float* w, float* sum) {
+        StreamStep st{};
+        st.S = p.streams; st.width = W; st.src = pend.src ? m->x : nullptr; st.y = pend.y; st.mix = pend.mix; st.out = pend.out;
+        st.mult = p.residual_mult; st.in = in; st.w = w; st.center = norm_center(m); st.eps = p.norm_eps; st.sum = sum;
+        if (m->f32) launch(m, lp_streams_kernel<float>, dim3(R), dim3(256), (size_t)W * 4, m->xs, st, (float*)m->hn);
+        else launch(m, lp_streams_kernel<bf16>, dim3(R), dim3(256), (size_t)W * 4, m->xs, st, (bf16*)m->hn);
+        pend = {nullptr, nullptr, nullptr, false};
+    };
+    const LayerPlan* cur = nullptr;   // the layer and the sublayer (0 mixer, 1 feed-forward) that project_in / project_out serve
+    int sub = 0;
     auto cast_x = [&](const float* y, const float* w) {
         if (m->f32) launch(m, lp_postnorm_kernel<float>, dim3(R), dim3(256), 0, m->x, y, w, (float*)m->hn, W, p.residual_alpha, p.norm_eps);
         else launch(m, lp_postnorm_kernel<bf16>, dim3(R), dim3(256), 0, m->x, y, w, (bf16*)m->hn, W, p.residual_alpha, p.norm_eps);
     };
     auto project_in = [&](const float* add, const float* nw, const void* Wm, int N, void* Y, int ldy, int epi) {
-        if (post) gemm(m, m->hn, W, Wm, N, W, Y, ldy, R, 1.0f, epi);
+        if (streams) {
+            boundary(cur->hc_in[sub], nw, nullptr);
+            gemm(m, m->hn, W, Wm, N, W, Y, ldy, R, 1.0f, epi);
+        } else if (post) gemm(m, m->hn, W, Wm, N, W, Y, ldy, R, 1.0f, epi);
         else norm_gemm(m, m->x, add, nullptr, nw, m->hn, Wm, N, Y, ldy, R, 1.0f, epi);
     };
     // Few rows (decoding) in the norm-after-sum form: the kernel that writes m->y also does what follows it -- its last block norms the
@@ -2171,13 +2433,16 @@ void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want,
         t.on = 1; t.x = m->x; t.y = m->y; t.w = nw; t.xc = m->hn; t.width = W; t.R = R; t.alpha = p.residual_alpha; t.eps = p.norm_eps;
         t.counter = m->tail_counter;
         if (moe) {
-            t.router = moe->w_up; t.E = moe->d.moe.experts; t.top = moe->d.moe.top;
+            t.router = moe->w_up; t.E = moe->d.moe.experts; t.top = moe->d.moe.top; t.route = moe->d.moe.route; t.route_scale = moe->d.moe.route_scale;
             t.logits = m->P; t.wts = m->moe_w; t.sel = m->moe_sel; t.selw = m->moe_selw;
         }
         return t;
     };
     auto project_out = [&](const void* X, int K, const void* Wm, const float* nw, const LayerPlan* moe) {
-        if (few) {
+        if (streams) {
+            gemm(m, X, K, Wm, W, K, m->y, W, R, 1.0f, EPI_STORE);
+            pend.y = m->y; pend.mix = cur->hc_mix[sub]; pend.out = cur->hc_out[sub];
+        } else if (few) {
             const RowsTail t = make_tail(nw, moe);
             gemm(m, X, K, Wm, W, K, m->y, W, R, 1.0f, EPI_STORE, &t);
         } else if (post) {
@@ -2193,6 +2458,8 @@ void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want,
         const bool moe_sel_ok = L.d.ff_kind == B200_FF_MOE && m->use_fuse && R <= 2 * GV_ROWS && W % (m->f32 ? 4 : 8) == 0 &&
                                 L.d.moe.expert_ff % (m->f32 ? 4 : 8) == 0 && L.d.moe.shared_ff % (m->f32 ? 4 : 8) == 0 && (size_t)R * W * elt(m) <= 48 * 1024;
         const LayerPlan* moe_next = (few && moe_sel_ok) ? &L : nullptr;      // the mixer's output kernel also routes
+        cur = &L;
+        sub = 0;
         project_in(add, L.norm1, L.w_in, L.n_in, m->P, L.n_in, EPI_STORE);
         if (L.d.mixer == B200_MIX_SOFTMAX_ATTN) {
             AttnGeom ag = L.ag;
@@ -2232,11 +2499,59 @@ void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want,
             if (m->f32) launch(m, lp_headnorm_gate_kernel<float>, hgrid, dim3(128), 0, (const float*)m->O, ldo, (const float*)m->P, L.n_in, L.dg.g_off, L.mem_norm, 0, mg.H, mg.vdim, p.norm_eps, 0, (float*)m->act_a + ag.H * ag.vdim, L.k_cat, L.d.mem_scale, R);
             else launch(m, lp_headnorm_gate_kernel<bf16>, hgrid, dim3(128), 0, (const float*)m->O, ldo, (const float*)m->P, L.n_in, L.dg.g_off, L.mem_norm, 0, mg.H, mg.vdim, p.norm_eps, 0, (bf16*)m->act_a + ag.H * ag.vdim, L.k_cat, L.d.mem_scale, R);
             project_out(m->act_a, L.k_cat, L.wo_cat, L.norm1, moe_next);
+        } else if (L.d.mixer == B200_MIX_LATENT_ATTN) {
+            // P = [W_dq h | W_dkv h | W_g h] -> norms, the cache row -> q = W_uq c_q -> rotated part and W_uk^T q_plain into qbuf ->
+            // attention over the cached rows (one shared K/V head, values inside the keys) -> W_uv per head -> gate -> W_o
+            const b200_latent_attn_desc& a = L.d.latent;
+            LatentGeom lg = L.lg;
+            lg.cache_off = m->run_kv_off[L.kv_layer == m->runs[run] ? run : (size_t)L.kv_layer];
+            const size_t csm = (size_t)lg.rot_n * 4;
+            const int per = a.dim + a.rot_dim, D = a.kv_rank + a.rot_dim, nv = a.heads * a.vdim;
+            if (m->f32) launch(m, lp_latent_prep_kernel<float>, dim3(R), dim3(256), csm, sm, lg, (const float*)m->P, L.n_in, L.dq_norm, L.dkv_norm, L.rot_freq, (float*)m->cq);
+            else launch(m, lp_latent_prep_kernel<bf16>, dim3(R), dim3(256), csm, sm, lg, (const float*)m->P, L.n_in, L.dq_norm, L.dkv_norm, L.rot_freq, (bf16*)m->cq);
+            gemm(m, m->cq, a.q_rank, L.w_uq, a.heads * per, a.q_rank, m->O, a.heads * per, R, 1.0f, EPI_STORE);
+            if (m->f32) launch(m, lp_latent_qprep_kernel<float>, dim3(R), dim3(256), csm, sm, lg, (const float*)m->O, L.rot_freq, (float*)m->act_a, m->qbuf);
+            else launch(m, lp_latent_qprep_kernel<bf16>, dim3(R), dim3(256), csm, sm, lg, (const float*)m->O, L.rot_freq, (bf16*)m->act_a, m->qbuf);
+            gemm_heads(m, m->act_a, a.heads * a.dim, a.dim, L.w_ukT, a.heads, a.kv_rank, a.dim, m->qbuf, a.heads * D, D, R);
+            AttnGeom ag = L.ag;
+            ag.kv_off = lg.cache_off;
+            ag.out_ld = a.heads * a.kv_rank;
+            ag.out_scale = 1.0f;
+            ag.fused_prep = 0;
+            if (!attn_tile(m, sm, ag, L.n_in, n_runs, max_len)) attn_rows(m, sm, ag, L, R);
+            gemm_heads(m, m->act_a, a.heads * a.kv_rank, a.kv_rank, L.w_uv, a.heads, a.vdim, a.kv_rank, m->O, nv, a.vdim, R);
+            const unsigned nb = (unsigned)(((size_t)R * nv + 255) / 256);
+            if (m->f32) launch(m, lp_latent_gate_kernel<float>, dim3(nb), dim3(256), 0, (const float*)m->O, (const float*)m->P, L.n_in, lg.g_off, a.out_gate, nv, R, (float*)m->act_a);
+            else launch(m, lp_latent_gate_kernel<bf16>, dim3(nb), dim3(256), 0, (const float*)m->O, (const float*)m->P, L.n_in, lg.g_off, a.out_gate, nv, R, (bf16*)m->act_a);
+            project_out(m->act_a, nv, L.wo, L.norm1, moe_next);
+        } else if (L.d.mixer == B200_MIX_STATE_SPACE) {
+            const b200_state_space_desc& g = L.d.ssd;
+            DeltaGeom dg = L.dg;
+            dg.rec_off = m->run_rec_off[run];
+            const int shift = (m->use_fuse && max_len == 1) ? 1 : 0;
+            launch(m, lp_conv_silu_kernel, dim3(R), dim3(256), 0, sm, dg, (const float*)m->P, L.n_in, L.conv_w, L.conv_b, m->conv, shift);
+            if (dg.taps > 1 && !shift) launch(m, lp_conv_tail_kernel, dim3(n_runs), dim3(256), 0, sm, dg, (const float*)m->P, L.n_in);
+            SsdGeom sg = L.sg;
+            sg.rec_off = dg.rec_off;
+            const int inner = g.heads * g.vdim;
+            const int dcols = SCAN_BD / (pick_dmax(g.state) / SCAN_DREG);
+            dim3 sgrid((g.vdim + dcols - 1) / dcols, g.heads, n_runs);
+#define LP_SSD(DM) launch(m, lp_ssd_scan_kernel<DM>, sgrid, dim3(SCAN_BD), 0, sm, sg, (const float*)m->conv, dg.C, (const float*)m->P, L.n_in, L.A_log, L.dt_bias, L.ssd_D, m->O, inner)
+            switch (pick_dmax(g.state)) {
+                case 32: LP_SSD(32); break;
+                case 64: LP_SSD(64); break;
+                case 128: LP_SSD(128); break;
+                default: LP_SSD(256); break;
+            }
+#undef LP_SSD
+            if (m->f32) launch(m, lp_gate_groupnorm_kernel<float>, dim3(R, g.norm_groups), dim3(256), 0, (const float*)m->O, inner, (const float*)m->P, L.n_in, 0, L.ssd_norm, inner, g.norm_groups, p.norm_eps, (float*)m->act_a);
+            else launch(m, lp_gate_groupnorm_kernel<bf16>, dim3(R, g.norm_groups), dim3(256), 0, (const float*)m->O, inner, (const float*)m->P, L.n_in, 0, L.ssd_norm, inner, g.norm_groups, p.norm_eps, (bf16*)m->act_a);
+            project_out(m->act_a, inner, L.wo, L.norm1, moe_next);
         } else {
             DeltaGeom dg = L.dg;
             dg.rec_off = m->run_rec_off[run];
             const int shift = (m->use_fuse && max_len == 1) ? 1 : 0;
-            launch(m, lp_conv_silu_kernel, dim3(R), dim3(256), 0, sm, dg, (const float*)m->P, L.n_in, L.conv_w, m->conv, shift);
+            launch(m, lp_conv_silu_kernel, dim3(R), dim3(256), 0, sm, dg, (const float*)m->P, L.n_in, L.conv_w, (const float*)nullptr, m->conv, shift);
             if (dg.taps > 1 && !shift) launch(m, lp_conv_tail_kernel, dim3(n_runs), dim3(256), 0, sm, dg, (const float*)m->P, L.n_in);
             const int ldo = dg.H * dg.vdim;
             const int dcols = SCAN_BD / (pick_dmax(dg.dim) / SCAN_DREG);
@@ -2257,10 +2572,13 @@ void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want,
             // Router logits (f32) -> the choice per row -> the experts -> m->y -> the residual.
             const b200_moe_desc& e = L.d.moe;
             const size_t es = elt(m);
-            if (!post) rmsnorm(m, m->x, nullptr, L.norm2, m->hn, nullptr, R);
+            const int act_epi = e.act == B200_ACT_GELU ? EPI_GELU : EPI_RELU2;
+            sub = 1;
+            if (streams) boundary(L.hc_in[1], L.norm2, nullptr);
+            else if (!post) rmsnorm(m, m->x, nullptr, L.norm2, m->hn, nullptr, R);
             if (!moe_next) {
                 gemm(m, m->hn, W, L.w_up, e.experts, W, m->P, e.experts, R, 1.0f, EPI_STORE);
-                launch(m, lp_moe_route_kernel, dim3((R + 3) / 4), dim3(128), 0, (const float*)m->P, e.experts, e.experts, e.top, m->moe_w, m->moe_sel, m->moe_selw, R);
+                launch(m, lp_moe_route_kernel, dim3((R + 3) / 4), dim3(128), 0, (const float*)m->P, e.experts, e.experts, e.top, m->moe_w, m->moe_sel, m->moe_selw, R, e.route, e.route_scale);
             }
             const size_t hbytes = (size_t)R * W * es;
             const uint8_t* up_experts = (const uint8_t*)L.w_up + (size_t)e.experts * W * es;
@@ -2272,10 +2590,10 @@ void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want,
                 const RowsTail t = few ? make_tail(L.norm2, nullptr) : RowsTail{};
                 normed = few;
                 if (m->f32) {
-                    launch(m, lp_moe_up_sel_kernel<float>, ugrid, dim3(256), hbytes, (const float*)m->hn, (const float*)L.w_up, (const int*)m->moe_sel, (const float*)m->moe_selw, e.experts, e.top, e.expert_ff, e.shared_ff, W, R, (float*)m->act_a);
+                    launch(m, lp_moe_up_sel_kernel<float>, ugrid, dim3(256), hbytes, (const float*)m->hn, (const float*)L.w_up, (const int*)m->moe_sel, (const float*)m->moe_selw, e.experts, e.top, e.expert_ff, e.shared_ff, W, R, (float*)m->act_a, e.act);
                     launch(m, lp_moe_down_sel_kernel<float>, dgrid, dim3(256), 0, (const float*)m->act_a, (const float*)L.w_down, (const int*)m->moe_sel, e.experts, e.top, e.expert_ff, e.shared_ff, W, R, m->y, t);
                 } else {
-                    launch(m, lp_moe_up_sel_kernel<bf16>, ugrid, dim3(256), hbytes, (const bf16*)m->hn, (const bf16*)L.w_up, (const int*)m->moe_sel, (const float*)m->moe_selw, e.experts, e.top, e.expert_ff, e.shared_ff, W, R, (bf16*)m->act_a);
+                    launch(m, lp_moe_up_sel_kernel<bf16>, ugrid, dim3(256), hbytes, (const bf16*)m->hn, (const bf16*)L.w_up, (const int*)m->moe_sel, (const float*)m->moe_selw, e.experts, e.top, e.expert_ff, e.shared_ff, W, R, (bf16*)m->act_a, e.act);
                     launch(m, lp_moe_down_sel_kernel<bf16>, dgrid, dim3(256), 0, (const bf16*)m->act_a, (const bf16*)L.w_down, (const int*)m->moe_sel, e.experts, e.top, e.expert_ff, e.shared_ff, W, R, m->y, t);
                 }
             } else if (m->use_fuse && R > 2 * GV_ROWS) {
@@ -2287,10 +2605,10 @@ void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want,
                 else launch(m, lp_moe_gather_kernel<bf16>, dim3(pairs), dim3(128), 0, (const bf16*)m->hn, (const int*)m->moe_pos, e.top, W, (bf16*)m->moe_xp);
                 const uint8_t* down = (const uint8_t*)L.w_down;
                 uint8_t* act_sh = (uint8_t*)m->act_a + (size_t)pairs * e.expert_ff * es;     // the always-on expert's activations behind the others
-                gemm_grouped(m, m->moe_xp, W, up_experts, W, (size_t)e.expert_ff * W, e.experts, e.expert_ff, W, m->act_a, e.expert_ff, R, EPI_RELU2, m->moe_seg);
+                gemm_grouped(m, m->moe_xp, W, up_experts, W, (size_t)e.expert_ff * W, e.experts, e.expert_ff, W, m->act_a, e.expert_ff, R, act_epi, m->moe_seg);
                 gemm_grouped(m, m->act_a, e.expert_ff, down, L.k_down, (size_t)e.expert_ff, e.experts, W, e.expert_ff, m->moe_yp, W, R, EPI_STORE, m->moe_seg);
                 if (e.shared_ff > 0) {
-                    gemm(m, m->hn, W, up_experts + (size_t)e.experts * e.expert_ff * W * es, e.shared_ff, W, act_sh, e.shared_ff, R, 1.0f, EPI_RELU2);
+                    gemm(m, m->hn, W, up_experts + (size_t)e.experts * e.expert_ff * W * es, e.shared_ff, W, act_sh, e.shared_ff, R, 1.0f, act_epi);
                     gemm_ld(m, act_sh, e.shared_ff, down + (size_t)e.experts * e.expert_ff * es, L.k_down, W, e.shared_ff, m->y, W, R, EPI_STORE);
                 }
                 launch(m, lp_moe_combine_kernel, dim3(R), dim3(256), 0, (const float*)m->moe_yp, (const int*)m->moe_pos, (const float*)m->moe_selw, e.top, W, e.shared_ff > 0 ? 1 : 0, m->y);
@@ -2300,27 +2618,33 @@ void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want,
                 const int n_exp = L.n_up - e.experts;
                 gemm(m, m->hn, W, up_experts, n_exp, W, m->P, n_exp, R, 1.0f, EPI_STORE);
                 const unsigned nb = (unsigned)(((size_t)R * L.k_down + 255) / 256);
-                if (m->f32) launch(m, lp_moe_act_kernel<float>, dim3(nb), dim3(256), 0, (const float*)m->P, n_exp, 0, (const float*)m->moe_w, e.experts, e.expert_ff, L.k_down, (float*)m->act_a, R);
-                else launch(m, lp_moe_act_kernel<bf16>, dim3(nb), dim3(256), 0, (const float*)m->P, n_exp, 0, (const float*)m->moe_w, e.experts, e.expert_ff, L.k_down, (bf16*)m->act_a, R);
+                if (m->f32) launch(m, lp_moe_act_kernel<float>, dim3(nb), dim3(256), 0, (const float*)m->P, n_exp, 0, (const float*)m->moe_w, e.experts, e.expert_ff, L.k_down, (float*)m->act_a, R, e.act);
+                else launch(m, lp_moe_act_kernel<bf16>, dim3(nb), dim3(256), 0, (const float*)m->P, n_exp, 0, (const float*)m->moe_w, e.experts, e.expert_ff, L.k_down, (bf16*)m->act_a, R, e.act);
                 gemm(m, m->act_a, L.k_down, L.w_down, W, L.k_down, m->y, W, R, 1.0f, EPI_STORE);
             }
             if (normed) {
+            } else if (streams) {
+                pend.y = m->y; pend.mix = L.hc_mix[1]; pend.out = L.hc_out[1];
             } else if (post) cast_x(m->y, L.norm2);
             else launch(m, lp_add_rows_kernel, dim3((unsigned)(((size_t)R * W + 255) / 256)), dim3(256), 0, m->x, (const float*)m->y, (size_t)R * W);
         } else if (L.d.ff > 0 && L.d.ff_kind == B200_FF_GATED_GELU) {
+            sub = 1;
             project_in(nullptr, L.norm2, L.w_up, L.n_up, m->P, L.n_up, EPI_STORE);
             const unsigned nb = (unsigned)(((size_t)R * L.d.ff + 255) / 256);
             if (m->f32) launch(m, lp_gated_gelu_kernel<float>, dim3(nb), dim3(256), 0, (const float*)m->P, L.n_up, (float*)m->act_a, L.d.ff, R);
             else launch(m, lp_gated_gelu_kernel<bf16>, dim3(nb), dim3(256), 0, (const float*)m->P, L.n_up, (bf16*)m->act_a, L.d.ff, R);
             project_out(m->act_a, L.d.ff, L.w_down, L.norm2, nullptr);
         } else if (L.d.ff > 0) {
+            sub = 1;
             project_in(nullptr, L.norm2, L.w_up, L.d.ff, m->act_a, L.d.ff, EPI_RELU2);
             project_out(m->act_a, L.d.ff, L.w_down, L.norm2, nullptr);
         } else if (post && L.norm2) {
             cast_x(nullptr, L.norm2);
         }
+        if (streams && taps_len > 0) boundary(nullptr, nullptr, m->x);   // the taps are the sum of the copies
         if (taps_len > 0) cudaMemcpyAsync(m->taps + run * (size_t)taps_len * W, m->x, (size_t)taps_len * W * 4, cudaMemcpyDeviceToDevice, m->stream);
     }
+    if (streams) boundary(nullptr, nullptr, m->x);   // the head reads the sum of the copies
     if (head) {
         norm_gemm(m, m->x, nullptr, sm.want, (const float*)find(m, "final.norm")->d, m->hw, find(m, "head")->d, p.vocab, m->logits, p.vocab, n_want,
                   p.logit_scale, EPI_STORE);

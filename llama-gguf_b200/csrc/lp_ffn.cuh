@@ -54,37 +54,41 @@ __global__ void lp_gated_gelu_kernel(const float* __restrict__ P, int ldp, OutT*
 
 // Router: one warp per row of the f32 logits P[r][0 .. E) (route_row, lp_rows_tail.cuh)
 __global__ void lp_moe_route_kernel(const float* __restrict__ P, int ldp, int E, int top, float* __restrict__ wts, int* __restrict__ sel,
-                                    float* __restrict__ selw, int R) {
+                                    float* __restrict__ selw, int R, int mode, float scale) {
     const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (r >= R) return;
-    route_row(P + (size_t)r * ldp, E, top, wts + (size_t)r * E, sel + (size_t)r * top, selw + (size_t)r * top, lane);
+    route_row(P + (size_t)r * ldp, E, top, wts + (size_t)r * E, sel + (size_t)r * top, selw + (size_t)r * top, lane, mode, scale);
 }
 
-// out[r][c] = relu(P[r][off + c])^2 * (weight of the expert that owns column c; 1 for the always-on expert's columns behind them)
+// an expert's activation: relu(z)^2 (B200_ACT_RELU2) or the exact GELU (B200_ACT_GELU)
+__device__ __forceinline__ float expert_act(float z, int act) {
+    if (act == B200_ACT_GELU) return gelu_erf_f(z);
+    z = fmaxf(z, 0.0f);
+    return z * z;
+}
+
+// out[r][c] = act(P[r][off + c]) * (weight of the expert that owns column c; 1 for the always-on expert's columns behind them)
 template <typename OutT>
 __global__ void lp_moe_act_kernel(const float* __restrict__ P, int ldp, int off, const float* __restrict__ wts, int E, int eff, int total,
-                                  OutT* __restrict__ out, int R) {
+                                  OutT* __restrict__ out, int R, int act) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (size_t)R * total) return;
     const int r = (int)(i / total), c = (int)(i - (size_t)r * total);
     const int e = c / eff;
     const float wgt = e < E ? wts[(size_t)r * E + e] : 1.0f;
     float v = 0.0f;
-    if (wgt != 0.0f) {
-        const float z = fmaxf(P[(size_t)r * ldp + off + c], 0.0f);
-        v = z * z * wgt;
-    }
+    if (wgt != 0.0f) v = expert_act(P[(size_t)r * ldp + off + c], act) * wgt;
     out[i] = from_f<OutT>(v);
 }
 
 // Few rows (decoding): only the chosen experts' weights are read.  up_cat holds [router | e0 up | e1 up | ... | always-on up] rows of
 // `width` columns; segment k < top of a row's activations belongs to expert sel[r][k], segment `top` to the always-on expert.
-//   act[r][k eff + n] = relu(up_e[n] . h_r)^2 * selw[r][k]        act[r][top eff + n] = relu(up_shared[n] . h_r)^2
+//   act[r][k eff + n] = act(up_e[n] . h_r) * selw[r][k]        act[r][top eff + n] = act(up_shared[n] . h_r),   act = relu^2 or GELU
 // One warp per (row, segment, n); h rows are staged in shared memory once per block.
 template <typename T>
 __global__ void __launch_bounds__(256) lp_moe_up_sel_kernel(const T* __restrict__ H, const T* __restrict__ up_cat, const int* __restrict__ sel,
                                                             const float* __restrict__ selw, int E, int top, int eff, int sff, int width, int R,
-                                                            T* __restrict__ act) {
+                                                            T* __restrict__ act, int act_kind) {
     extern __shared__ __align__(16) uint8_t mu_smem[];
     T* hs = reinterpret_cast<T*>(mu_smem);
     constexpr int VN = Vec8<T>::N;
@@ -110,10 +114,7 @@ __global__ void __launch_bounds__(256) lp_moe_up_sel_kernel(const T* __restrict_
             for (int j = 0; j < VN; j++) acc = fmaf(wv[j], xv[j], acc);
         }
         acc = wsum(acc);
-        if (lane == 0) {
-            const float z = fmaxf(acc, 0.0f);
-            act[o] = from_f<T>(z * z * (k < top ? selw[(size_t)r * top + k] : 1.0f));
-        }
+        if (lane == 0) act[o] = from_f<T>(expert_act(acc, act_kind) * (k < top ? selw[(size_t)r * top + k] : 1.0f));
     }
 }
 

@@ -5,13 +5,22 @@
 #pragma once
 
 // Router of a mixture of experts for one row, by one warp: the `top` largest of z[0 .. E) are taken one after the other (of equal
-// logits the lower index first); their weights are the softmax over the chosen logits only.  w[e] receives the weight of expert e
-// (0 when it is not chosen); sel[k] / selw[k] list the chosen experts in the order they were taken.
+// logits the lower index first); their weights are the softmax over the chosen logits only (mode B200_ROUTE_TOP_SOFTMAX), or their
+// share of the softmax over ALL experts times `scale`, not renormalised (B200_ROUTE_SOFTMAX_TOP).  w[e] receives the weight of
+// expert e (0 when it is not chosen); sel[k] / selw[k] list the chosen experts in the order they were taken.
 __device__ __forceinline__ void route_row(const float* __restrict__ z, int E, int top, float* __restrict__ w, int* __restrict__ sel,
-                                          float* __restrict__ selw, int lane) {
+                                          float* __restrict__ selw, int lane, int mode, float scale) {
     for (int e = lane; e < E; e += 32) w[e] = 0.0f;
     __syncwarp();
     float zmax = 0.0f, sum = 0.0f;
+    float all = 0.0f;
+    if (mode == B200_ROUTE_SOFTMAX_TOP) {
+        float mx = -INFINITY;
+        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
+        mx = wmax(mx);
+        for (int e = lane; e < E; e += 32) all += expf(z[e] - mx);
+        all = wsum(all);
+    }
     for (int k = 0; k < top; k++) {
         float best = -INFINITY;
         int bi = 0x7fffffff;
@@ -35,7 +44,7 @@ __device__ __forceinline__ void route_row(const float* __restrict__ z, int E, in
         }
         __syncwarp();
     }
-    const float inv = 1.0f / sum;
+    const float inv = mode == B200_ROUTE_SOFTMAX_TOP ? scale / all : 1.0f / sum;
     for (int e = lane; e < E; e += 32)
         if (w[e] != 0.0f) w[e] = (-1.0f - w[e]) * inv;
     for (int k = lane; k < top; k += 32) selw[k] *= inv;
@@ -53,6 +62,8 @@ struct RowsTail {
     unsigned* counter;                  // zero before the launch; the last block sets it back
     const void* router;                 // [E][width] in the compute type, or null
     int E, top;
+    int route;                          // B200_ROUTE_*
+    float route_scale;
     float *logits, *wts, *selw;         // [R][E], [R][E], [R][top]
     int* sel;                           // [R][top]
 };
@@ -150,7 +161,7 @@ __device__ void rows_tail(const RowsTail& t) {
         }
         __syncthreads();
         for (int r = warp; r < t.R; r += nw)
-            route_row(t.logits + (size_t)r * t.E, t.E, t.top, t.wts + (size_t)r * t.E, t.sel + (size_t)r * t.top, t.selw + (size_t)r * t.top, lane);
+            route_row(t.logits + (size_t)r * t.E, t.E, t.top, t.wts + (size_t)r * t.E, t.sel + (size_t)r * t.top, t.selw + (size_t)r * t.top, lane, t.route, t.route_scale);
     }
     if (threadIdx.x == 0) *t.counter = 0u;
 }

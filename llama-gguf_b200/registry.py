@@ -19,7 +19,12 @@ def _mefurax(path, **kw):
     return mefurax.load(path, **kw)
 
 
-LOADERS = {"Lazilorn": _lazilorn, "Mefurax": _mefurax}
+def _madudra(path, **kw):
+    from . import madudra
+    return madudra.load(path, **kw)
+
+
+LOADERS = {"Lazilorn": _lazilorn, "Mefurax": _mefurax, "Madudra": _madudra}
 
 
 def architecture_of(path):
