@@ -1,7 +1,8 @@
-"""bench.py --design lazilorn | mefurax: prefill and decode throughput of a layer-program design at sizes that resemble a real model's
+"""bench.py --design lazilorn | mefurax | madudra: prefill and decode throughput of a layer-program design at sizes that resemble a real model's
 layers (random weights), beside the library's closest existing model -- a llama-architecture transformer of the same width, depth
 and parameter count in Q8_0 blocks (the densest weight type its tensor-core prompt path takes); Mefurax also beside Lazilorn at
-the same width and depth (the other bf16 layer program, whose attention and GEMM kernels it shares).
+the same width and depth (the other bf16 layer program, whose attention and GEMM kernels it shares); Madudra beside Lazilorn (the
+other hybrid of attention and recurrent scans) and Mefurax (the other mixture of experts) at the same width and depth.
 
 Per size and model: prompt tokens/s for one prompt of --prefill-len tokens, decode tokens/s at batch 1 and at --batch sequences
 after prompts of --prompt-len tokens.  Every number is host wall clock around the library call (each call ends with a stream
@@ -57,6 +58,33 @@ def mefurax_config(s, span=1024):
     return {"architecture": "Mefurax", "width": s["width"], "vocab": s["vocab"], "norm": {"eps": 1e-6}, "postln_alpha": 2.0, "layers": layers}
 
 
+MADUDRA_SIZES = {
+    # name: width, layers (l = latent attention with its own cache rows, k = latent attention on layer 0's rows, m = state-space mixer; every
+    # layer with a mixture of experts), attention heads, query latent, state-space heads, experts / chosen / expert ff, residual streams
+    "w1024": dict(width=1024, pattern="lmmkmm", heads=8, q_rank=512, ssd_heads=16, experts=8, top=2, eff=1024, streams=4, vocab=32000),
+    "w2048": dict(width=2048, pattern="lmmkmmkm", heads=16, q_rank=768, ssd_heads=32, experts=8, top=2, eff=2048, streams=4, vocab=32000),
+}
+
+
+def madudra_config(s, span=1024):
+    # cached row = 96 latent + 32 rotated = 128 floats (the width the tile attention kernel takes); heads of 64 + 32 query / key and 128
+    # value channels; state-space heads of 128 channels with 128 state rows (inner = 2 x width)
+    layers = []
+    mlp = {"kind": "moe", "router": {"experts": s["experts"], "top": s["top"], "scale": 1.0}, "expert": {"ff": s["eff"]}}
+    for ch in s["pattern"]:
+        if ch == "m":
+            layers.append({"type": "mamba2", "mlp": mlp,
+                           "mixer": {"heads": s["ssd_heads"], "vdim": 128, "state": 128, "groups": 1, "conv": 4, "norm_groups": 1}})
+            continue
+        m = {"heads": s["heads"], "dim": 64, "rot_dim": 32, "vdim": 128, "q_rank": s["q_rank"], "kv_rank": 96, "mask": {"size": span},
+             "scale": 96 ** -0.5, "rot": {"dims": 32, "base": 10000.0, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+        if ch == "k":
+            m["kv_from"] = 0
+        layers.append({"type": "latent_attention", "mixer": m, "mlp": mlp})
+    return {"architecture": "Madudra", "width": s["width"], "vocab": s["vocab"], "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
+            "residual_mult": 0.5, "streams": s["streams"], "layers": layers}
+
+
 def lazilorn_feeder(cfg, seed, tensor_shapes=None):
     """upload(name, type, ne, data) for every tensor of cfg: bf16 bit patterns of N(0, 1/fan_in) matrices, f32 vectors."""
     import llama_gguf_b200 as B
@@ -68,6 +96,11 @@ def lazilorn_feeder(cfg, seed, tensor_shapes=None):
         rng = np.random.default_rng(seed)
         for name, shape in tensor_shapes(cfg).items():
             last = name.split(".")[-1]
+            if ".hc" in name:      # stream weights near the plain residual
+                a = {"mix": lambda: np.eye(shape[0]) + 0.05 * rng.standard_normal(shape), "in": lambda: np.full(shape, 1.0 / shape[0]),
+                     "out": lambda: np.ones(shape)}[last]()
+                upload(name, B.F32, list(reversed(shape)), np.ascontiguousarray(a, dtype=np.float32))
+                continue
             if len(shape) == 2 and last != "conv" and name != "loop.step":
                 a = rng.standard_normal(shape, dtype=np.float32) * np.float32(1.0 / np.sqrt(shape[-1]))
                 upload(name, B.BF16, list(reversed(shape)), bf16_bits(a).reshape(shape))
@@ -87,8 +120,8 @@ def lazilorn_feeder(cfg, seed, tensor_shapes=None):
 
 
 def design_module(cfg):
-    from llama_gguf_b200 import lazilorn, mefurax
-    return {"Lazilorn": lazilorn, "Mefurax": mefurax}[cfg["architecture"]]
+    from llama_gguf_b200 import lazilorn, madudra, mefurax
+    return {"Lazilorn": lazilorn, "Mefurax": mefurax, "Madudra": madudra}[cfg["architecture"]]
 
 
 def n_params(cfg):
@@ -178,6 +211,8 @@ def main(args):
         return 2
     if args.design == "mefurax":
         return main_mefurax(args)
+    if args.design == "madudra":
+        return main_madudra(args)
     sizes = [x for x in (args.sizes.split(",") if args.sizes else SIZES) if x]
     max_seq = max(args.prefill_len, args.prompt_len + args.warmup + args.steps + 8) + 8
     res = {}
@@ -222,4 +257,26 @@ def main_mefurax(args):
     print(json.dumps({"bench": "design", "design": "mefurax", "unit": "tok/s", "prefill_len": args.prefill_len, "prompt_len": args.prompt_len,
                       "batch": args.batch, "steps": args.steps, "warmup": args.warmup, "timing": "host wall clock around the library calls",
                       "dtype": "bf16 (mefurax, lazilorn) / Q8_0 (llama, sized to mefurax's active parameters)", "data": "synthetic", "sizes": res}))
+    return 0
+
+
+def main_madudra(args):
+    sizes = [x for x in (args.sizes.split(",") if args.sizes else MADUDRA_SIZES) if x]
+    max_seq = max(args.prefill_len, args.prompt_len + args.warmup + args.steps + 8) + 8
+    res = {}
+    for name in sizes:
+        s = MADUDRA_SIZES[name]
+        cfg = madudra_config(s)
+        params = n_params(cfg)
+        active = params - len(s["pattern"]) * (s["experts"] - s["top"]) * 2 * s["width"] * s["eff"]
+        r = {"params_without_embedding": params, "active_params_without_embedding": active, "layers": s["pattern"],
+             "madudra_bf16": bench_lazilorn(cfg, args, max_seq)}
+        print(name, json.dumps(r), file=sys.stderr, flush=True)
+        r["lazilorn_bf16"] = bench_lazilorn(lazilorn_config(SIZES[name]), args, max_seq)
+        r["mefurax_bf16"] = bench_lazilorn(mefurax_config(MEFURAX_SIZES[name]), args, max_seq)
+        res[name] = r
+        print(name, json.dumps(r), file=sys.stderr, flush=True)
+    print(json.dumps({"bench": "design", "design": "madudra", "unit": "tok/s", "prefill_len": args.prefill_len, "prompt_len": args.prompt_len,
+                      "batch": args.batch, "steps": args.steps, "warmup": args.warmup, "timing": "host wall clock around the library calls",
+                      "dtype": "bf16 (madudra, lazilorn, mefurax at the same width and depth)", "data": "synthetic", "sizes": res}))
     return 0
