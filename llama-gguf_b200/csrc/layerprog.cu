@@ -1115,7 +1115,7 @@ __global__ void lp_conv_silu_kernel(StepMeta sm, DeltaGeom g, const float* __res
     const int t = r - sm.run_start[run];
     float* tail = reinterpret_cast<float*>(sm.run_rec[run] + g.rec_off) + (size_t)g.H * g.dim * g.vdim;
     P += g.in_off;
-    for (int c = threadIdx.x; c < g.C; c += blockDim.x) {
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < g.C; c += gridDim.y * blockDim.x) {   // (channels are independent)
         float y = bias ? bias[c] : 0.0f;
         for (int i = 0; i < g.taps; i++) {
             const int tt = t - (g.taps - 1) + i;
@@ -1134,7 +1134,7 @@ __global__ void lp_conv_tail_kernel(StepMeta sm, DeltaGeom g, const float* __res
     const int run = blockIdx.x, r0 = sm.run_start[run], len = sm.run_start[run + 1] - r0;
     float* tail = reinterpret_cast<float*>(sm.run_rec[run] + g.rec_off) + (size_t)g.H * g.dim * g.vdim;
     P += g.in_off;
-    for (int c = threadIdx.x; c < g.C; c += blockDim.x)
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < g.C; c += gridDim.y * blockDim.x)
         for (int i = 0; i < g.taps - 1; i++) {
             const int st = len + i - (g.taps - 1);
             tail[(size_t)i * g.C + c] = st >= 0 ? P[(size_t)(r0 + st) * ldp + c] : tail[(size_t)(i + len) * g.C + c];
@@ -2216,8 +2216,10 @@ int lp_finalize(LpModel* m, std::string* err) {
     if (p.streams > 0) {   // the stream kernel keeps a row of the width in shared memory
         if ((size_t)p.width * 4 > 200 * 1024) return lp_fail(err, B200_ERR_UNSUPPORTED, "multi-stream form: a row exceeds 200 KB of shared memory");
         if ((size_t)p.width * 4 > 48 * 1024) {
-            LCU(cudaFuncSetAttribute(lp_streams_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, p.width * 4));
-            LCU(cudaFuncSetAttribute(lp_streams_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, p.width * 4));
+            LCU(cudaFuncSetAttribute(lp_streams_kernel<float, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, p.width * 4));
+            LCU(cudaFuncSetAttribute(lp_streams_kernel<float, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, p.width * 4));
+            LCU(cudaFuncSetAttribute(lp_streams_kernel<bf16, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, p.width * 4));
+            LCU(cudaFuncSetAttribute(lp_streams_kernel<bf16, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, p.width * 4));
         }
     }
     LCU_ALLOC(cudaMalloc((void**)&m->tc_err, 256));
@@ -2408,8 +2410,14 @@ void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want,
         StreamStep st{};
         st.S = p.streams; st.width = W; st.src = pend.src ? m->x : nullptr; st.y = pend.y; st.mix = pend.mix; st.out = pend.out;
         st.mult = p.residual_mult; st.in = in; st.w = w; st.center = norm_center(m); st.eps = p.norm_eps; st.sum = sum;
-        if (m->f32) launch(m, lp_streams_kernel<float>, dim3(R), dim3(256), (size_t)W * 4, m->xs, st, (float*)m->hn);
-        else launch(m, lp_streams_kernel<bf16>, dim3(R), dim3(256), (size_t)W * 4, m->xs, st, (bf16*)m->hn);
+        const bool v4 = W % 4 == 0 && (!sum || ((uintptr_t)sum & 15) == 0);
+        if (m->f32) {
+            if (v4) launch(m, lp_streams_kernel<float, 4>, dim3(R), dim3(256), (size_t)W * 4, m->xs, st, (float*)m->hn);
+            else launch(m, lp_streams_kernel<float, 1>, dim3(R), dim3(256), (size_t)W * 4, m->xs, st, (float*)m->hn);
+        } else {
+            if (v4) launch(m, lp_streams_kernel<bf16, 4>, dim3(R), dim3(256), (size_t)W * 4, m->xs, st, (bf16*)m->hn);
+            else launch(m, lp_streams_kernel<bf16, 1>, dim3(R), dim3(256), (size_t)W * 4, m->xs, st, (bf16*)m->hn);
+        }
         pend = {nullptr, nullptr, nullptr, false};
     };
     const LayerPlan* cur = nullptr;   // the layer and the sublayer (0 mixer, 1 feed-forward) that project_in / project_out serve
@@ -2529,8 +2537,8 @@ void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want,
             DeltaGeom dg = L.dg;
             dg.rec_off = m->run_rec_off[run];
             const int shift = (m->use_fuse && max_len == 1) ? 1 : 0;
-            launch(m, lp_conv_silu_kernel, dim3(R), dim3(256), 0, sm, dg, (const float*)m->P, L.n_in, L.conv_w, L.conv_b, m->conv, shift);
-            if (dg.taps > 1 && !shift) launch(m, lp_conv_tail_kernel, dim3(n_runs), dim3(256), 0, sm, dg, (const float*)m->P, L.n_in);
+            launch(m, lp_conv_silu_kernel, dim3(R, (dg.C + 255) / 256), dim3(256), 0, sm, dg, (const float*)m->P, L.n_in, L.conv_w, L.conv_b, m->conv, shift);
+            if (dg.taps > 1 && !shift) launch(m, lp_conv_tail_kernel, dim3(n_runs, (dg.C + 255) / 256), dim3(256), 0, sm, dg, (const float*)m->P, L.n_in);
             SsdGeom sg = L.sg;
             sg.rec_off = dg.rec_off;
             const int inner = g.heads * g.vdim;
@@ -2551,8 +2559,8 @@ void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want,
             DeltaGeom dg = L.dg;
             dg.rec_off = m->run_rec_off[run];
             const int shift = (m->use_fuse && max_len == 1) ? 1 : 0;
-            launch(m, lp_conv_silu_kernel, dim3(R), dim3(256), 0, sm, dg, (const float*)m->P, L.n_in, L.conv_w, (const float*)nullptr, m->conv, shift);
-            if (dg.taps > 1 && !shift) launch(m, lp_conv_tail_kernel, dim3(n_runs), dim3(256), 0, sm, dg, (const float*)m->P, L.n_in);
+            launch(m, lp_conv_silu_kernel, dim3(R, (dg.C + 255) / 256), dim3(256), 0, sm, dg, (const float*)m->P, L.n_in, L.conv_w, (const float*)nullptr, m->conv, shift);
+            if (dg.taps > 1 && !shift) launch(m, lp_conv_tail_kernel, dim3(n_runs, (dg.C + 255) / 256), dim3(256), 0, sm, dg, (const float*)m->P, L.n_in);
             const int ldo = dg.H * dg.vdim;
             const int dcols = SCAN_BD / (pick_dmax(dg.dim) / SCAN_DREG);
             dim3 sgrid((dg.vdim + dcols - 1) / dcols, dg.H, n_runs);

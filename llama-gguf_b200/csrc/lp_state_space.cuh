@@ -62,7 +62,8 @@ __global__ void __launch_bounds__(SCAN_BD) lp_ssd_scan_kernel(StepMeta sm, SsdGe
         }
         cp_async_wait_all();
         __syncthreads();
-        for (int t = 0; t < nt; t++) {
+#pragma unroll 4
+        for (int t = 0; t < nt; t++) {   // (unrolled: only the state's one multiply-add per token is serial, the read-outs overlap)
             const float decay = dec_s[t], x = xs_[t][col], dx = dt_s[t] * x;
             float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
 #pragma unroll
@@ -99,10 +100,26 @@ __global__ void __launch_bounds__(256) lp_gate_groupnorm_kernel(const float* __r
     const int r = blockIdx.x, gi = blockIdx.y, len = n / groups, c0 = gi * len;
     const float* o = O + (size_t)r * ldo + c0;
     const float* z = P + (size_t)r * ldp + z_off + c0;
+    // four channels per thread and load when everything is 16-byte aligned (the gated values stay in registers for rows up to 4096)
+    const bool v4 = (len & 3) == 0 && (ldo & 3) == 0 && (ldp & 3) == 0 && ((z_off + c0) & 3) == 0 && (c0 & 3) == 0 && len <= 4 * 4 * 256;
+    float4 keep[4];
     float ss = 0.0f;
-    for (int c = threadIdx.x; c < len; c += blockDim.x) {
-        const float v = o[c] * (z[c] * sigmoid_f(z[c]));
-        ss = fmaf(v, v, ss);
+    if (v4) {
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const int c = (threadIdx.x + u * 256) * 4;
+            keep[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (c < len) {
+                const float4 a = *reinterpret_cast<const float4*>(o + c), g = *reinterpret_cast<const float4*>(z + c);
+                keep[u] = make_float4(a.x * (g.x * sigmoid_f(g.x)), a.y * (g.y * sigmoid_f(g.y)), a.z * (g.z * sigmoid_f(g.z)), a.w * (g.w * sigmoid_f(g.w)));
+                ss += keep[u].x * keep[u].x + keep[u].y * keep[u].y + keep[u].z * keep[u].z + keep[u].w * keep[u].w;
+            }
+        }
+    } else {
+        for (int c = threadIdx.x; c < len; c += blockDim.x) {
+            const float v = o[c] * (z[c] * sigmoid_f(z[c]));
+            ss = fmaf(v, v, ss);
+        }
     }
     ss = wsum(ss);
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
@@ -114,6 +131,21 @@ __global__ void __launch_bounds__(256) lp_gate_groupnorm_kernel(const float* __r
     }
     __syncthreads();
     const float inv = red[8];
+    if (v4) {
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const int c = (threadIdx.x + u * 256) * 4;
+            if (c < len) {
+                const float4 wv = *reinterpret_cast<const float4*>(w + c0 + c);
+                OutT* dst = out + (size_t)r * n + c0 + c;
+                dst[0] = from_f<OutT>(keep[u].x * inv * wv.x);
+                dst[1] = from_f<OutT>(keep[u].y * inv * wv.y);
+                dst[2] = from_f<OutT>(keep[u].z * inv * wv.z);
+                dst[3] = from_f<OutT>(keep[u].w * inv * wv.w);
+            }
+        }
+        return;
+    }
     for (int c = threadIdx.x; c < len; c += blockDim.x) {
         const float v = o[c] * (z[c] * sigmoid_f(z[c]));
         out[(size_t)r * n + c0 + c] = from_f<OutT>(v * inv * w[c0 + c]);

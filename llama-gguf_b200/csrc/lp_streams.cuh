@@ -20,12 +20,25 @@ struct StreamStep {
     float* sum;              // [R][width]: receives the plain sum of the streams, or null
 };
 
-// One block per row.  xs [R][S][width].  Pass 1, per channel: the S old values -> the S new ones (stored), their weighted sum u into
-// shared memory.  Pass 2: mean and variance of u over the row (two passes over shared memory: the variance is the mean of the squared
-// deviations), hn = (u - mean) / sqrt(var + eps) * w.
-template <typename OutT>
+// One block per row.  xs [R][S][width].  Pass 1, per group of VEC channels (VEC = 4: 16-byte loads and stores, the width a multiple of
+// 4): the S old values -> the S new ones (all loads of a group before its stores), their weighted sum u into shared memory.  Pass 2:
+// mean and variance of u over the row (two passes over shared memory: the variance is the mean of the squared deviations),
+// hn = (u - mean) / sqrt(var + eps) * w.
+template <int VEC>
+__device__ __forceinline__ void st_load(const float* p, float* o) {
+    if (VEC == 4) {
+        const float4 v = *reinterpret_cast<const float4*>(p);
+        o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w;
+    } else o[0] = *p;
+}
+template <int VEC>
+__device__ __forceinline__ void st_store(float* p, const float* o) {
+    if (VEC == 4) *reinterpret_cast<float4*>(p) = make_float4(o[0], o[1], o[2], o[3]);
+    else *p = o[0];
+}
+template <typename OutT, int VEC>
 __global__ void __launch_bounds__(256) lp_streams_kernel(float* __restrict__ xs, StreamStep st, OutT* __restrict__ hn) {
-    extern __shared__ float u_s[];      // [width]
+    extern __shared__ __align__(16) float u_s[];      // [width]
     __shared__ float red[9];
     __shared__ float mix_s[ST_MAX * ST_MAX], out_s[ST_MAX], in_s[ST_MAX];
     const int r = blockIdx.x, S = st.S, W = st.width, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
@@ -36,43 +49,62 @@ __global__ void __launch_bounds__(256) lp_streams_kernel(float* __restrict__ xs,
     }
     __syncthreads();
     float* xr = xs + (size_t)r * S * W;
+    const float* __restrict__ src = st.src ? st.src + (size_t)r * W : nullptr;
+    const float* __restrict__ yr = st.y ? st.y + (size_t)r * W : nullptr;
+    float* __restrict__ sum = st.sum ? st.sum + (size_t)r * W : nullptr;
     float tot = 0.0f;
-    for (int c = threadIdx.x; c < W; c += blockDim.x) {
-        float v[ST_MAX];
-        if (st.src) {
-            const float e = st.src[(size_t)r * W + c];
+    for (int c = threadIdx.x * VEC; c < W; c += blockDim.x * VEC) {
+        float v[ST_MAX][VEC], yv[VEC], nv[ST_MAX][VEC], u[VEC], plain[VEC];
+        if (src) {
+            st_load<VEC>(src + c, v[0]);
 #pragma unroll
-            for (int s = 0; s < ST_MAX; s++) v[s] = e;
+            for (int s = 1; s < ST_MAX; s++)
+#pragma unroll
+                for (int k = 0; k < VEC; k++) v[s][k] = v[0][k];
         } else {
 #pragma unroll
-            for (int s = 0; s < ST_MAX; s++) v[s] = s < S ? xr[(size_t)s * W + c] : 0.0f;
+            for (int s = 0; s < ST_MAX; s++) {
+                if (s < S) st_load<VEC>(xr + (size_t)s * W + c, v[s]);
+                else
+#pragma unroll
+                    for (int k = 0; k < VEC; k++) v[s][k] = 0.0f;
+            }
         }
-        if (st.y) {
-            const float yv = st.y[(size_t)r * W + c];
-            float nv[ST_MAX];
+        if (yr) {
+            st_load<VEC>(yr + c, yv);
 #pragma unroll
             for (int t = 0; t < ST_MAX; t++) {
-                float a = 0.0f;
 #pragma unroll
-                for (int s = 0; s < ST_MAX; s++)
-                    if (s < S && t < S) a = fmaf(mix_s[s * S + t], v[s], a);
-                nv[t] = t < S ? fmaf(out_s[t], yv, a) : 0.0f;
+                for (int k = 0; k < VEC; k++) {
+                    float a = 0.0f;
+#pragma unroll
+                    for (int s = 0; s < ST_MAX; s++)
+                        if (s < S && t < S) a = fmaf(mix_s[s * S + t], v[s][k], a);
+                    nv[t][k] = t < S ? fmaf(out_s[t], yv[k], a) : 0.0f;
+                }
             }
 #pragma unroll
-            for (int t = 0; t < ST_MAX; t++) v[t] = nv[t];
+            for (int t = 0; t < ST_MAX; t++)
+#pragma unroll
+                for (int k = 0; k < VEC; k++) v[t][k] = nv[t][k];
         }
-        float u = 0.0f, plain = 0.0f;
+#pragma unroll
+        for (int k = 0; k < VEC; k++) u[k] = plain[k] = 0.0f;
 #pragma unroll
         for (int s = 0; s < ST_MAX; s++) {
             if (s < S) {
-                if (st.y || st.src) xr[(size_t)s * W + c] = v[s];
-                u = fmaf(in_s[s], v[s], u);
-                plain += v[s];
+                if (yr || src) st_store<VEC>(xr + (size_t)s * W + c, v[s]);
+#pragma unroll
+                for (int k = 0; k < VEC; k++) {
+                    u[k] = fmaf(in_s[s], v[s][k], u[k]);
+                    plain[k] += v[s][k];
+                }
             }
         }
-        if (st.sum) st.sum[(size_t)r * W + c] = plain;
-        u_s[c] = u;
-        tot += u;
+        if (sum) st_store<VEC>(sum + c, plain);
+        st_store<VEC>(u_s + c, u);
+#pragma unroll
+        for (int k = 0; k < VEC; k++) tot += u[k];
     }
     if (!st.w) return;
     auto block_sum = [&](float v) {
@@ -90,10 +122,18 @@ __global__ void __launch_bounds__(256) lp_streams_kernel(float* __restrict__ xs,
     };
     const float mean = st.center ? block_sum(tot) / (float)W : 0.0f;
     float sq = 0.0f;
-    for (int c = threadIdx.x; c < W; c += blockDim.x) {   // (a thread reads back its own entries of u_s)
-        const float d = u_s[c] - mean;
-        sq = fmaf(d, d, sq);
+    for (int c = threadIdx.x * VEC; c < W; c += blockDim.x * VEC) {   // (a thread reads back its own entries of u_s)
+#pragma unroll
+        for (int k = 0; k < VEC; k++) {
+            const float d = u_s[c + k] - mean;
+            sq = fmaf(d, d, sq);
+        }
     }
     const float inv = 1.0f / sqrtf(block_sum(sq) / (float)W + st.eps);
-    for (int c = threadIdx.x; c < W; c += blockDim.x) hn[(size_t)r * W + c] = from_f<OutT>((u_s[c] - mean) * inv * st.w[c]);
+    for (int c = threadIdx.x * VEC; c < W; c += blockDim.x * VEC) {
+        float wv[VEC];
+        st_load<VEC>(st.w + c, wv);
+#pragma unroll
+        for (int k = 0; k < VEC; k++) hn[(size_t)r * W + c + k] = from_f<OutT>((u_s[c + k] - mean) * inv * wv[k]);
+    }
 }
