@@ -1400,6 +1400,7 @@ struct LpModel {
     bool use_tc = true;
     bool use_fuse = true;        // B200_LP_FUSE=0: every step of a layer as a kernel of its own (norm, projection, ...)
     bool use_attn_tile = true;   // B200_LP_ATTN_TILE=0: the warp kernel for prompts too
+    bool use_stream_tail = true; // B200_LP_STREAM_TAIL=0: few rows of the multi-stream form launch lp_streams_kernel instead of the fused tails
     // decode steps replay a CUDA graph per (rows, wanted rows, head); a graph is void once a scratch buffer has moved (B200_LP_GRAPH=0: eager)
     struct Graph { cudaGraphExec_t exec = nullptr; uint64_t launches = 0, epoch = 0; bool warm = false; };
     std::map<uint64_t, Graph> graphs;
@@ -1749,6 +1750,8 @@ int lp_create(const b200_program_desc* prog, const b200_layer_desc* layers, int 
         if (e && *e) m->use_fuse = atoi(e) != 0;
         e = getenv("B200_LP_ATTN_TILE");
         if (e && *e) m->use_attn_tile = atoi(e) != 0;
+        e = getenv("B200_LP_STREAM_TAIL");
+        if (e && *e) m->use_stream_tail = atoi(e) != 0;
         e = getenv("B200_LP_GRAPH");
         if (e && *e) m->use_graph = atoi(e) != 0;
         e = getenv("B200_LP_TC_MIN_ROWS");
@@ -2216,10 +2219,15 @@ int lp_finalize(LpModel* m, std::string* err) {
     if (p.streams > 0) {   // the stream kernel keeps a row of the width in shared memory
         if ((size_t)p.width * 4 > 200 * 1024) return lp_fail(err, B200_ERR_UNSUPPORTED, "multi-stream form: a row exceeds 200 KB of shared memory");
         if ((size_t)p.width * 4 > 48 * 1024) {
-            LCU(cudaFuncSetAttribute(lp_streams_kernel<float, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, p.width * 4));
-            LCU(cudaFuncSetAttribute(lp_streams_kernel<float, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, p.width * 4));
-            LCU(cudaFuncSetAttribute(lp_streams_kernel<bf16, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, p.width * 4));
-            LCU(cudaFuncSetAttribute(lp_streams_kernel<bf16, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, p.width * 4));
+            const int sb = p.width * 4;
+            LCU(cudaFuncSetAttribute(lp_streams_kernel<float, 1, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, sb));
+            LCU(cudaFuncSetAttribute(lp_streams_kernel<float, 4, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, sb));
+            LCU(cudaFuncSetAttribute(lp_streams_kernel<bf16, 1, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, sb));
+            LCU(cudaFuncSetAttribute(lp_streams_kernel<bf16, 4, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, sb));
+            LCU(cudaFuncSetAttribute(lp_streams_kernel<float, 1, ST_MAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, sb));
+            LCU(cudaFuncSetAttribute(lp_streams_kernel<float, 4, ST_MAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, sb));
+            LCU(cudaFuncSetAttribute(lp_streams_kernel<bf16, 1, ST_MAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, sb));
+            LCU(cudaFuncSetAttribute(lp_streams_kernel<bf16, 4, ST_MAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, sb));
         }
     }
     LCU_ALLOC(cudaMalloc((void**)&m->tc_err, 256));
@@ -2406,22 +2414,56 @@ void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want,
         const float *y, *mix, *out;
         bool src;
     } pend = {nullptr, nullptr, nullptr, true};
+    // Few rows (decoding): the kernel that writes m->y also does what follows it -- its last block updates the copies and norms the
+    // next input, and when a mixture comes next it routes (rows_tail); the next call of `boundary` then finds its work done.
+    // (one block works through the rows one after the other: measured level with the separate launch for one row, 20 % behind it for
+    // eight, so only the smallest steps take it)
+    const bool sfew = streams && m->use_fuse && m->use_stream_tail && R <= 2 && taps_len == 0;
+    bool pre_done = false;
     auto boundary = [&](const float* in, const float* w, float* sum) {
+        if (pre_done) {
+            pre_done = false;
+            pend = {nullptr, nullptr, nullptr, false};
+            return;
+        }
         StreamStep st{};
         st.S = p.streams; st.width = W; st.src = pend.src ? m->x : nullptr; st.y = pend.y; st.mix = pend.mix; st.out = pend.out;
         st.mult = p.residual_mult; st.in = in; st.w = w; st.center = norm_center(m); st.eps = p.norm_eps; st.sum = sum;
-        const bool v4 = W % 4 == 0 && (!sum || ((uintptr_t)sum & 15) == 0);
+        const bool v4 = W % 4 == 0 && (!sum || ((uintptr_t)sum & 15) == 0), few_s = p.streams <= 4;
+#define LP_ST(T, V, SM) launch(m, lp_streams_kernel<T, V, SM>, dim3(R), dim3(256), (size_t)W * 4, m->xs, st, (T*)m->hn)
         if (m->f32) {
-            if (v4) launch(m, lp_streams_kernel<float, 4>, dim3(R), dim3(256), (size_t)W * 4, m->xs, st, (float*)m->hn);
-            else launch(m, lp_streams_kernel<float, 1>, dim3(R), dim3(256), (size_t)W * 4, m->xs, st, (float*)m->hn);
+            if (v4 && few_s) LP_ST(float, 4, 4); else if (v4) LP_ST(float, 4, ST_MAX); else if (few_s) LP_ST(float, 1, 4); else LP_ST(float, 1, ST_MAX);
         } else {
-            if (v4) launch(m, lp_streams_kernel<bf16, 4>, dim3(R), dim3(256), (size_t)W * 4, m->xs, st, (bf16*)m->hn);
-            else launch(m, lp_streams_kernel<bf16, 1>, dim3(R), dim3(256), (size_t)W * 4, m->xs, st, (bf16*)m->hn);
+            if (v4 && few_s) LP_ST(bf16, 4, 4); else if (v4) LP_ST(bf16, 4, ST_MAX); else if (few_s) LP_ST(bf16, 1, 4); else LP_ST(bf16, 1, ST_MAX);
         }
+#undef LP_ST
         pend = {nullptr, nullptr, nullptr, false};
     };
     const LayerPlan* cur = nullptr;   // the layer and the sublayer (0 mixer, 1 feed-forward) that project_in / project_out serve
     int sub = 0;
+    size_t cur_run = 0;
+    bool cur_moe_sel = false;
+    // the tail of the kernel that ends sublayer `sub` of the current layer: what the sublayer after it reads
+    auto stream_tail = [&]() {
+        RowsTail t{};
+        t.on = 1; t.streams = 1; t.xs = m->xs; t.xc = m->hn; t.width = W; t.R = R; t.counter = m->tail_counter;
+        StreamStep& st = t.st;
+        st.S = p.streams; st.width = W; st.y = m->y; st.mix = cur->hc_mix[sub]; st.out = cur->hc_out[sub]; st.mult = p.residual_mult;
+        st.center = norm_center(m); st.eps = p.norm_eps;
+        const bool has_ff = cur->d.ff_kind == B200_FF_MOE || cur->d.ff > 0;
+        if (sub == 0 && has_ff) {
+            st.in = cur->hc_in[1]; st.w = cur->norm2;
+            if (cur->d.ff_kind == B200_FF_MOE && cur_moe_sel) {
+                const b200_moe_desc& e = cur->d.moe;
+                t.router = cur->w_up; t.E = e.experts; t.top = e.top; t.route = e.route; t.route_scale = e.route_scale;
+                t.logits = m->P; t.wts = m->moe_w; t.sel = m->moe_sel; t.selw = m->moe_selw;
+            }
+        } else if (cur_run + 1 < m->runs.size()) {
+            const LayerPlan& nx = m->plan[m->runs[cur_run + 1]];
+            st.in = nx.hc_in[0]; st.w = nx.norm1;
+        } else st.sum = m->x;   // the head reads the sum of the copies
+        return t;
+    };
     auto cast_x = [&](const float* y, const float* w) {
         if (m->f32) launch(m, lp_postnorm_kernel<float>, dim3(R), dim3(256), 0, m->x, y, w, (float*)m->hn, W, p.residual_alpha, p.norm_eps);
         else launch(m, lp_postnorm_kernel<bf16>, dim3(R), dim3(256), 0, m->x, y, w, (bf16*)m->hn, W, p.residual_alpha, p.norm_eps);
@@ -2447,7 +2489,11 @@ void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want,
         return t;
     };
     auto project_out = [&](const void* X, int K, const void* Wm, const float* nw, const LayerPlan* moe) {
-        if (streams) {
+        if (sfew) {
+            const RowsTail t = stream_tail();
+            gemm(m, X, K, Wm, W, K, m->y, W, R, 1.0f, EPI_STORE, &t);
+            pre_done = true;
+        } else if (streams) {
             gemm(m, X, K, Wm, W, K, m->y, W, R, 1.0f, EPI_STORE);
             pend.y = m->y; pend.mix = cur->hc_mix[sub]; pend.out = cur->hc_out[sub];
         } else if (few) {
@@ -2465,9 +2511,11 @@ void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want,
         // the few-row expert kernels (16-byte loads: sizes multiples of 8 / 4, the rows in shared memory)
         const bool moe_sel_ok = L.d.ff_kind == B200_FF_MOE && m->use_fuse && R <= 2 * GV_ROWS && W % (m->f32 ? 4 : 8) == 0 &&
                                 L.d.moe.expert_ff % (m->f32 ? 4 : 8) == 0 && L.d.moe.shared_ff % (m->f32 ? 4 : 8) == 0 && (size_t)R * W * elt(m) <= 48 * 1024;
-        const LayerPlan* moe_next = (few && moe_sel_ok) ? &L : nullptr;      // the mixer's output kernel also routes
+        const LayerPlan* moe_next = ((few || sfew) && moe_sel_ok) ? &L : nullptr;      // the mixer's output kernel also routes
         cur = &L;
         sub = 0;
+        cur_run = run;
+        cur_moe_sel = moe_sel_ok;
         project_in(add, L.norm1, L.w_in, L.n_in, m->P, L.n_in, EPI_STORE);
         if (L.d.mixer == B200_MIX_SOFTMAX_ATTN) {
             AttnGeom ag = L.ag;
@@ -2595,8 +2643,9 @@ void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want,
                 // few rows (decoding): kernels that walk each row's choices and read those experts' weights only
                 const int per_row = e.top * e.expert_ff + e.shared_ff;
                 dim3 ugrid(std::min((R * per_row + 7) / 8, 8 * 148)), dgrid(std::min((R * W + 1) / 2, 8 * 148));
-                const RowsTail t = few ? make_tail(L.norm2, nullptr) : RowsTail{};
-                normed = few;
+                const RowsTail t = sfew ? stream_tail() : few ? make_tail(L.norm2, nullptr) : RowsTail{};
+                normed = few || sfew;
+                if (sfew) pre_done = true;
                 if (m->f32) {
                     launch(m, lp_moe_up_sel_kernel<float>, ugrid, dim3(256), hbytes, (const float*)m->hn, (const float*)L.w_up, (const int*)m->moe_sel, (const float*)m->moe_selw, e.experts, e.top, e.expert_ff, e.shared_ff, W, R, (float*)m->act_a, e.act);
                     launch(m, lp_moe_down_sel_kernel<float>, dgrid, dim3(256), 0, (const float*)m->act_a, (const float*)L.w_down, (const int*)m->moe_sel, e.experts, e.top, e.expert_ff, e.shared_ff, W, R, m->y, t);

@@ -51,8 +51,28 @@ __device__ __forceinline__ void route_row(const float* __restrict__ z, int E, in
     __syncwarp();
 }
 
+// What the multi-stream layer form does between two sublayers (lp_streams.cuh has the kernel for many rows; rows_tail below does
+// the same for few rows inside the kernel that wrote y).
+constexpr int ST_MAX = 8;   // streams at most (they live in registers)
+struct StreamStep {
+    int S, width;
+    const float* src;        // [R][width]: every stream starts as this row (the embedding); null: the streams hold their values
+    const float* y;          // [R][width] output of the sublayer before, or null
+    const float* mix;        // [S][S] (from, to) of that sublayer, null = identity
+    const float* out;        // [S], null = ones
+    float mult;              // factor on y
+    const float* in;         // [S] weights of the next sublayer's input, null = ones (the plain sum)
+    const float* w;          // norm weight of the next sublayer, null = no norm and no compute-type copy
+    int center;              // 1: layer norm (mean taken off), 0: RMS norm
+    float eps;
+    float* sum;              // [R][width]: receives the plain sum of the streams, or null
+};
+
 struct RowsTail {
     int on;                             // 0: the kernel ends as usual
+    int streams;                        // 1: the multi-stream form: `st` says what to do with y, xs holds the copies [R][S][width]
+    StreamStep st;
+    float* xs;
     float* x;                           // [R][width] residual stream, f32
     const float* y;                     // [R][width] what the kernel's blocks have written
     const float* w;                     // norm weight
@@ -83,10 +103,162 @@ __device__ void rows_tail(const RowsTail& t) {
     __threadfence();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;   // (blockDim.x = 256)
     T* xc = reinterpret_cast<T*>(t.xc);
+    if (t.streams) {
+        // Row by row, the whole block: the copies are updated from y (pass 1, which also sums the next input u), then u is formed
+        // twice more from the copies this thread has just written (no row buffer: the kernel's shared memory belongs to its main
+        // part) for the variance and for the normed row.
+        const StreamStep& st = t.st;
+        const int S = st.S, W = st.width;
+        __shared__ float mix_s[ST_MAX * ST_MAX], out_s[ST_MAX], in_s[ST_MAX];
+        __shared__ float tot_s;
+        if (threadIdx.x < S * S) mix_s[threadIdx.x] = st.mix ? st.mix[threadIdx.x] : (threadIdx.x / S == threadIdx.x % S ? 1.0f : 0.0f);
+        if (threadIdx.x < S) {
+            out_s[threadIdx.x] = (st.out ? st.out[threadIdx.x] : 1.0f) * st.mult;
+            in_s[threadIdx.x] = st.in ? st.in[threadIdx.x] : 1.0f;
+        }
+        __syncthreads();
+        auto block_sum = [&](float v) {
+            v = wsum(v);
+            __syncthreads();
+            if (lane == 0) part[warp] = v;
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                float a = 0.0f;
+                for (int i = 0; i < nw; i++) a += part[i];
+                tot_s = a;
+            }
+            __syncthreads();
+            return tot_s;
+        };
+        // Rows up to 4096 wide (a multiple of 4): a thread owns up to TG groups of 4 channels; all their loads are issued before the
+        // first store, and the next input u stays in registers for the variance and the normed row.
+        constexpr int TG = 4;
+        const bool fast = (W & 3) == 0 && W <= 4 * 256 * TG && S <= 4;
+        for (int r = 0; r < (fast ? t.R : 0); r++) {
+            float* xr = t.xs + (size_t)r * S * W;
+            const float* yr = st.y + (size_t)r * W;
+            float4 v[TG][4], yv[TG];
+            float u[TG][4];
+#pragma unroll
+            for (int g = 0; g < TG; g++) {
+                const int c = (threadIdx.x + g * 256) * 4;
+                if (c < W) {
+                    yv[g] = __ldcg(reinterpret_cast<const float4*>(yr + c));
+#pragma unroll
+                    for (int s = 0; s < 4; s++)
+                        v[g][s] = s < S ? *reinterpret_cast<const float4*>(xr + (size_t)s * W + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+            }
+            float tot = 0.0f;
+#pragma unroll
+            for (int g = 0; g < TG; g++) {
+                const int c = (threadIdx.x + g * 256) * 4;
+                u[g][0] = u[g][1] = u[g][2] = u[g][3] = 0.0f;
+                if (c < W) {
+                    const float y4[4] = {yv[g].x, yv[g].y, yv[g].z, yv[g].w};
+                    float o4[4][4], plain[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        float a[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                        for (int s = 0; s < 4; s++) {
+                            if (s < S && k < S) {
+                                const float mx = mix_s[s * S + k];
+                                a[0] = fmaf(mx, v[g][s].x, a[0]);
+                                a[1] = fmaf(mx, v[g][s].y, a[1]);
+                                a[2] = fmaf(mx, v[g][s].z, a[2]);
+                                a[3] = fmaf(mx, v[g][s].w, a[3]);
+                            }
+                        }
+#pragma unroll
+                        for (int e = 0; e < 4; e++) o4[k][e] = k < S ? fmaf(out_s[k], y4[e], a[e]) : 0.0f;
+                    }
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        if (k < S) {
+                            *reinterpret_cast<float4*>(xr + (size_t)k * W + c) = make_float4(o4[k][0], o4[k][1], o4[k][2], o4[k][3]);
+#pragma unroll
+                            for (int e = 0; e < 4; e++) {
+                                u[g][e] = fmaf(in_s[k], o4[k][e], u[g][e]);
+                                plain[e] += o4[k][e];
+                            }
+                        }
+                    }
+                    if (st.sum) *reinterpret_cast<float4*>(st.sum + (size_t)r * W + c) = make_float4(plain[0], plain[1], plain[2], plain[3]);
+                    tot += (u[g][0] + u[g][1]) + (u[g][2] + u[g][3]);
+                }
+            }
+            if (!st.w) continue;
+            const float mean = st.center ? block_sum(tot) / (float)W : 0.0f;
+            float sq = 0.0f;
+#pragma unroll
+            for (int g = 0; g < TG; g++)
+                if ((threadIdx.x + g * 256) * 4 < W)
+#pragma unroll
+                    for (int e = 0; e < 4; e++) sq = fmaf(u[g][e] - mean, u[g][e] - mean, sq);
+            const float inv = 1.0f / sqrtf(block_sum(sq) / (float)W + st.eps);
+#pragma unroll
+            for (int g = 0; g < TG; g++) {
+                const int c = (threadIdx.x + g * 256) * 4;
+                if (c < W) {
+                    const float4 wv = *reinterpret_cast<const float4*>(st.w + c);
+                    const float w4[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+                    for (int e = 0; e < 4; e++) xc[(size_t)r * W + c + e] = from_f<T>((u[g][e] - mean) * inv * w4[e]);
+                }
+            }
+        }
+        for (int r = 0; r < (fast ? 0 : t.R); r++) {
+            float* xr = t.xs + (size_t)r * S * W;
+            const float* yr = st.y + (size_t)r * W;
+            float tot = 0.0f;
+            for (int c = threadIdx.x; c < W; c += blockDim.x) {
+                float v[ST_MAX], nv[ST_MAX];
+#pragma unroll
+                for (int s = 0; s < ST_MAX; s++) v[s] = s < S ? xr[(size_t)s * W + c] : 0.0f;
+                const float yv = __ldcg(yr + c);
+                float u = 0.0f, plain = 0.0f;
+#pragma unroll
+                for (int k = 0; k < ST_MAX; k++) {
+                    float a = 0.0f;
+#pragma unroll
+                    for (int s = 0; s < ST_MAX; s++)
+                        if (s < S && k < S) a = fmaf(mix_s[s * S + k], v[s], a);
+                    nv[k] = k < S ? fmaf(out_s[k], yv, a) : 0.0f;
+                }
+#pragma unroll
+                for (int s = 0; s < ST_MAX; s++) {
+                    if (s < S) {
+                        xr[(size_t)s * W + c] = nv[s];
+                        u = fmaf(in_s[s], nv[s], u);
+                        plain += nv[s];
+                    }
+                }
+                if (st.sum) st.sum[(size_t)r * W + c] = plain;
+                tot += u;
+            }
+            if (!st.w) continue;
+            auto u_of = [&](int c) {
+                float u = 0.0f;
+#pragma unroll
+                for (int s = 0; s < ST_MAX; s++)
+                    if (s < S) u = fmaf(in_s[s], xr[(size_t)s * W + c], u);
+                return u;
+            };
+            const float mean = st.center ? block_sum(tot) / (float)W : 0.0f;
+            float sq = 0.0f;
+            for (int c = threadIdx.x; c < W; c += blockDim.x) {   // (a thread reads back its own writes)
+                const float d = u_of(c) - mean;
+                sq = fmaf(d, d, sq);
+            }
+            const float inv = 1.0f / sqrtf(block_sum(sq) / (float)W + st.eps);
+            for (int c = threadIdx.x; c < W; c += blockDim.x) xc[(size_t)r * W + c] = from_f<T>((u_of(c) - mean) * inv * st.w[c]);
+        }
+    }
     int wpr = nw;
     while (wpr > 1 && nw / wpr < t.R) wpr >>= 1;
     const int rows_par = nw / wpr, grp = warp / wpr, tig = (warp % wpr) * 32 + lane, T_ = wpr * 32;
-    for (int r0 = 0; r0 < t.R; r0 += rows_par) {
+    for (int r0 = 0; r0 < (t.streams ? 0 : t.R); r0 += rows_par) {
         const int r = r0 + grp;
         const bool live = r < t.R;
         float* xr = t.x + (size_t)(live ? r : 0) * t.width;
@@ -135,7 +307,7 @@ __device__ void rows_tail(const RowsTail& t) {
             }
         }
     }
-    if (t.router) {
+    if (t.router && (!t.streams || t.st.w)) {
         __syncthreads();                                // the copies of all rows are in place (this block wrote them)
         const T* rw = reinterpret_cast<const T*>(t.router);
         constexpr int VN = Vec8<T>::N;

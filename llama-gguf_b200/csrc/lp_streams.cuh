@@ -4,21 +4,7 @@
 // inside its anonymous namespace.  Everything is f32; the normed row is rounded once to the compute type.
 #pragma once
 
-constexpr int ST_MAX = 8;   // streams at most (they live in registers)
-
-struct StreamStep {
-    int S, width;
-    const float* src;        // [R][width]: every stream starts as this row (the embedding); null: the streams hold their values
-    const float* y;          // [R][width] output of the sublayer before, or null
-    const float* mix;        // [S][S] (from, to) of that sublayer, null = identity
-    const float* out;        // [S], null = ones
-    float mult;              // factor on y
-    const float* in;         // [S] weights of the next sublayer's input, null = ones (the plain sum)
-    const float* w;          // norm weight of the next sublayer, null = no norm and no compute-type copy
-    int center;              // 1: layer norm (mean taken off), 0: RMS norm
-    float eps;
-    float* sum;              // [R][width]: receives the plain sum of the streams, or null
-};
+// (StreamStep: lp_rows_tail.cuh)
 
 // One block per row.  xs [R][S][width].  Pass 1, per group of VEC channels (VEC = 4: 16-byte loads and stores, the width a multiple of
 // 4): the S old values -> the S new ones (all loads of a group before its stores), their weighted sum u into shared memory.  Pass 2:
@@ -36,7 +22,8 @@ __device__ __forceinline__ void st_store(float* p, const float* o) {
     if (VEC == 4) *reinterpret_cast<float4*>(p) = make_float4(o[0], o[1], o[2], o[3]);
     else *p = o[0];
 }
-template <typename OutT, int VEC>
+// (SMAX: compile-time bound of the stream count, 4 or ST_MAX, so that few streams cost few registers)
+template <typename OutT, int VEC, int SMAX>
 __global__ void __launch_bounds__(256) lp_streams_kernel(float* __restrict__ xs, StreamStep st, OutT* __restrict__ hn) {
     extern __shared__ __align__(16) float u_s[];      // [width]
     __shared__ float red[9];
@@ -54,16 +41,16 @@ __global__ void __launch_bounds__(256) lp_streams_kernel(float* __restrict__ xs,
     float* __restrict__ sum = st.sum ? st.sum + (size_t)r * W : nullptr;
     float tot = 0.0f;
     for (int c = threadIdx.x * VEC; c < W; c += blockDim.x * VEC) {
-        float v[ST_MAX][VEC], yv[VEC], nv[ST_MAX][VEC], u[VEC], plain[VEC];
+        float v[SMAX][VEC], yv[VEC], nv[SMAX][VEC], u[VEC], plain[VEC];
         if (src) {
             st_load<VEC>(src + c, v[0]);
 #pragma unroll
-            for (int s = 1; s < ST_MAX; s++)
+            for (int s = 1; s < SMAX; s++)
 #pragma unroll
                 for (int k = 0; k < VEC; k++) v[s][k] = v[0][k];
         } else {
 #pragma unroll
-            for (int s = 0; s < ST_MAX; s++) {
+            for (int s = 0; s < SMAX; s++) {
                 if (s < S) st_load<VEC>(xr + (size_t)s * W + c, v[s]);
                 else
 #pragma unroll
@@ -73,25 +60,25 @@ __global__ void __launch_bounds__(256) lp_streams_kernel(float* __restrict__ xs,
         if (yr) {
             st_load<VEC>(yr + c, yv);
 #pragma unroll
-            for (int t = 0; t < ST_MAX; t++) {
+            for (int t = 0; t < SMAX; t++) {
 #pragma unroll
                 for (int k = 0; k < VEC; k++) {
                     float a = 0.0f;
 #pragma unroll
-                    for (int s = 0; s < ST_MAX; s++)
+                    for (int s = 0; s < SMAX; s++)
                         if (s < S && t < S) a = fmaf(mix_s[s * S + t], v[s][k], a);
                     nv[t][k] = t < S ? fmaf(out_s[t], yv[k], a) : 0.0f;
                 }
             }
 #pragma unroll
-            for (int t = 0; t < ST_MAX; t++)
+            for (int t = 0; t < SMAX; t++)
 #pragma unroll
                 for (int k = 0; k < VEC; k++) v[t][k] = nv[t][k];
         }
 #pragma unroll
         for (int k = 0; k < VEC; k++) u[k] = plain[k] = 0.0f;
 #pragma unroll
-        for (int s = 0; s < ST_MAX; s++) {
+        for (int s = 0; s < SMAX; s++) {
             if (s < S) {
                 if (yr || src) st_store<VEC>(xr + (size_t)s * W + c, v[s]);
 #pragma unroll
