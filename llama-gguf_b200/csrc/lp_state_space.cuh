@@ -42,14 +42,25 @@ __global__ void __launch_bounds__(SCAN_BD) lp_ssd_scan_kernel(StepMeta sm, SsdGe
     const float rate = expf(A_log[h]), dtb = dt_bias[h], dskip = Dskip[h];
     const int inner = g.H * g.vdim, b_col = inner + grp * g.N, c_col = inner + g.G * g.N + grp * g.N;
     const int jc = blockIdx.x * COLS + (tid % COLS);
+    const bool vec = ((g.N | ldc | b_col | c_col) & 3) == 0 && (reinterpret_cast<uintptr_t>(XBC) & 15) == 0;
     for (int c0 = r0; c0 < r1; c0 += CH) {
         const int nt = min(CH, r1 - c0);
         __syncthreads();
-        for (int t = 0; t < nt; t++) {
-            const float* x = XBC + (size_t)(c0 + t) * ldc;
-            for (int d = tid; d < g.N; d += SCAN_BD) {
-                cp_async4(&bs_[t][d], x + b_col + d);
-                cp_async4(&cs_[t][d], x + c_col + d);
+        if (vec) {   // 16-byte copies: a token's B and C rows are N / 4 chunks each
+            const int per = g.N >> 2;
+            for (int i = tid; i < nt * per; i += SCAN_BD) {
+                const int t = i / per, d = (i - t * per) * 4;
+                const float* x = XBC + (size_t)(c0 + t) * ldc;
+                cp_async16(smem_u32(&bs_[t][d]), x + b_col + d, 16u);
+                cp_async16(smem_u32(&cs_[t][d]), x + c_col + d, 16u);
+            }
+        } else {
+            for (int t = 0; t < nt; t++) {
+                const float* x = XBC + (size_t)(c0 + t) * ldc;
+                for (int d = tid; d < g.N; d += SCAN_BD) {
+                    cp_async4(&bs_[t][d], x + b_col + d);
+                    cp_async4(&cs_[t][d], x + c_col + d);
+                }
             }
         }
         for (int t = tid / COLS; t < nt; t += SPLIT) {
