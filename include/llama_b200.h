@@ -286,11 +286,33 @@ B200_API const char* b200_batch_last_error(b200_batch* batch);   /* message of t
  *          '.conv.b') + SiLU over [x | B | C]; dt = softplus(dt + dt_bias); per head (group floor(head * groups / heads)):
  *          S <- exp(-exp(A_log) dt) S + dt B x^T (S: state x vdim, f32, zero at the start), y = S^T C + D x; then y * silu(z), rms norm
  *          in norm_groups equal parts times '.norm', W_o.  A slot's state block holds S and the last conv - 1 inputs of the convolution.
+ *   B200_MIX_ATTN_RECURRENT two branches on the same normed input ('.mix.left.*' and '.mix.right.*'): left the general softmax mixer
+ *          (`sattn`, every option of B200_MIX_SOFTMAX_ATTN but value blending), right a recurrent unit chosen by rec_kind:
+ *          B200_REC_GATED_LINEAR (b200_gated_linear_desc): a matrix memory per head whose forget gate also says what is written,
+ *          q = silu(W_q h), v = W_v h, f = l + (1 - l) sigmoid(W_f h + '.f.b') with the stored lower bound l = '.lower' (heads * dim),
+ *          S <- diag(f) S + (1 - f) v^T (S: dim x vdim, f32, zero at the start), o = S^T q, rms norm per head times '.norm' (vdim);
+ *          B200_REC_GATED_UNIT (b200_gated_unit_desc): one state per channel, z = sigmoid(W_z h + '.z.b'), u = W_x h + '.x.b',
+ *          s <- (1 - z) s + z c with c = u + 1/2 (u >= 0) or sigmoid(u) (u < 0), output s * silu(W_g h).
+ *          Both go through their own W_o.  combine = B200_COMBINE_WEIGHTED: attn_scale * left + mem_scale * right (one product over
+ *          [left | right]); B200_COMBINE_NORMED_MEAN: each branch's projected output is rms-normed over the width with its plain
+ *          weight '.left.out' / '.right.out' and the mixer is half their sum.
+ * Options of the softmax mixer beyond those above (b200_softmax_attn_desc): mask B200_MASK_CAUSAL (every earlier position); stretched
+ * rotary frequencies (yarn_*, as in b200_rotary_desc); rot_after_norm = 1: the q / k norm comes before the rotation; v_rot_base > 0:
+ * the values carry positions, v_j is turned by j over all its pairs (2m, 2m + 1) with the angle j * v_rot_base^(-2m / vdim) before it
+ * is cached and a head's summed output at position i is turned back by -i; sink: the softmax's denominator holds one more term
+ * exp(c) without key or value, c = '.sink'[head] (B200_SINK_LEARNED) or c = 0 (B200_SINK_ZERO); o_bias: '.o.b' is added by the output
+ * projection.
  * Feed-forward (ff_kind): B200_FF_RELU2 W_down relu(W_up h)^2 of width ff (none when ff = 0); B200_FF_GATED_GELU W_down (gelu_tanh(W_gate h)
  * * W_up h) of width ff; B200_FF_MOE: router logits W_router h in f32, the `top` largest are chosen and weighted by the softmax over
  * the chosen logits, experts W_down relu(W_up h)^2 of width expert_ff, plus an always-on expert of width shared_ff (0 = none);
  * moe.route = B200_ROUTE_SOFTMAX_TOP: softmax over ALL experts, the `top` largest taken and weighted by their probability times
  * route_scale, not renormalised; moe.act = B200_ACT_GELU: experts W_down gelu(W_up h) with the exact (erf) GELU.
+ * B200_FF_CLAMPED_GLU: g = min(W_gate h, ff_limit), u = clamp(W_up h, +-ff_limit), W_down (g sigmoid(ff_slope g) (u + 1)) of width ff.
+ * moe.route = B200_ROUTE_SIGMOID_TOP: scores sigmoid(logit), the `top` largest taken with their scores as weights (times route_scale
+ * when it is not 0), not renormalised; moe.act = B200_ACT_SILU_GLU: gated experts W_down (silu(W_gate .) * W_up .) ('.e<j>.gate');
+ * moe.weight_input = 1: the weight multiplies the expert's input, sum_e expert_e(w_e h), instead of its output.
+ * parallel_ff = 1 (with post_norm = 0, streams = 0): a layer has one norm and its feed-forward reads the mixer's input,
+ * h = norm1(x), x += mixer(h) + ff(h); the layer's input projection then also holds the feed-forward's ([gate | up] or the router).
  * Layer form (program): post_norm = 0: x += sublayer(norm(x)); post_norm = 1: x <- norm(residual_alpha * x + sublayer(x)), the
  * sublayers read x itself.  Norm weights are applied as (norm_weight_offset + w).  norm_kind = B200_NORM_LAYER: the layer norms and
  * the final norm subtract the mean first, (x - mean) / sqrt(var + eps) * w (no bias), instead of the RMS norm.
@@ -301,16 +323,20 @@ B200_API const char* b200_batch_last_error(b200_batch* batch);   /* message of t
  * Embedding: row * embed_scale (+ sinusoidal position vector, pos_sinusoid); logits = head . norm(x) * logit_scale.
  * compute: 0 = bf16 weights and GEMM operands with f32 accumulation (residual stream, norms, softmax, gates and every recurrent
  * state stay f32), 1 = everything in f32 (FMA, no reduced-precision matrix mode). */
-enum { B200_MIX_WINDOW_MEMORY = 1, B200_MIX_GATED_DELTA = 2, B200_MIX_SOFTMAX_ATTN = 3, B200_MIX_LATENT_ATTN = 4, B200_MIX_STATE_SPACE = 5 };
-enum { B200_MASK_WINDOW = 0, B200_MASK_CHUNK = 1 };
+enum { B200_MIX_WINDOW_MEMORY = 1, B200_MIX_GATED_DELTA = 2, B200_MIX_SOFTMAX_ATTN = 3, B200_MIX_LATENT_ATTN = 4, B200_MIX_STATE_SPACE = 5,
+       B200_MIX_ATTN_RECURRENT = 6 };
+enum { B200_MASK_WINDOW = 0, B200_MASK_CHUNK = 1, B200_MASK_CAUSAL = 2 };
+enum { B200_SINK_NONE = 0, B200_SINK_LEARNED = 1, B200_SINK_ZERO = 2 };
+enum { B200_REC_GATED_LINEAR = 1, B200_REC_GATED_UNIT = 2 };
+enum { B200_COMBINE_WEIGHTED = 0, B200_COMBINE_NORMED_MEAN = 1 };
 enum { B200_QKNORM_NONE = 0, B200_QKNORM_HEAD_WEIGHT = 1, B200_QKNORM_WHOLE_WEIGHT = 2, B200_QKNORM_HEAD_UNIT = 3 };
 enum { B200_GATE_NONE = 0, B200_GATE_CHANNEL = 1, B200_GATE_HEAD = 2 };
 enum { B200_VMIX_NONE = 0, B200_VMIX_SOURCE = 1, B200_VMIX_BLEND = 2 };
-enum { B200_FF_RELU2 = 0, B200_FF_GATED_GELU = 1, B200_FF_MOE = 2 };
+enum { B200_FF_RELU2 = 0, B200_FF_GATED_GELU = 1, B200_FF_MOE = 2, B200_FF_CLAMPED_GLU = 3 };
 enum { B200_COMPUTE_BF16 = 0, B200_COMPUTE_F32 = 1 };
 enum { B200_NORM_RMS = 0, B200_NORM_LAYER = 1 };
-enum { B200_ACT_RELU2 = 0, B200_ACT_GELU = 1 };
-enum { B200_ROUTE_TOP_SOFTMAX = 0, B200_ROUTE_SOFTMAX_TOP = 1 };
+enum { B200_ACT_RELU2 = 0, B200_ACT_GELU = 1, B200_ACT_SILU_GLU = 2 };
+enum { B200_ROUTE_TOP_SOFTMAX = 0, B200_ROUTE_SOFTMAX_TOP = 1, B200_ROUTE_SIGMOID_TOP = 2 };
 enum { B200_TYPE_BF16 = 30 };   /* ggml's id; accepted by layer-program contexts only */
 typedef struct b200_window_attn_desc {
     int32_t heads, kv_heads, dim, vdim;
@@ -337,12 +363,18 @@ typedef struct b200_softmax_attn_desc {
     float softcap;                   /* 0 = none */
     float dist_bias_exp;             /* 0 = none */
     int32_t v_mix, out_gate;         /* B200_VMIX_*, B200_GATE_* ('.g': [heads * vdim, width] or [heads, width]) */
+    float yarn_factor, yarn_original, yarn_fast, yarn_slow;   /* stretched frequencies of the q / k rotation; factor 0 = plain */
+    int32_t rot_after_norm;          /* 1 = norm first, then the rotation */
+    float v_rot_base;                /* > 0: values are turned by their position and the summed output is turned back */
+    int32_t sink;                    /* B200_SINK_* */
+    int32_t o_bias;                  /* 1 = '.o.b' is added by the output projection */
 } b200_softmax_attn_desc;
 typedef struct b200_moe_desc {
     int32_t experts, top, expert_ff, shared_ff;
     int32_t act;                     /* B200_ACT_* of the experts */
     int32_t route;                   /* B200_ROUTE_* */
     float route_scale;               /* B200_ROUTE_SOFTMAX_TOP: factor on the chosen probabilities */
+    int32_t weight_input;            /* 1 = an expert's weight multiplies its input instead of its output */
 } b200_moe_desc;
 /* Rotary frequencies: f_i = base^(-2i / dims), i < dims / 2.  yarn_factor > 0 stretches long wavelengths: with
  * d(t) = dims ln(yarn_original / (2 pi t)) / (2 ln base), lo = max(floor(d(yarn_fast)), 0), hi = min(ceil(d(yarn_slow)), dims - 1) and
@@ -365,6 +397,12 @@ typedef struct b200_latent_attn_desc {
 typedef struct b200_state_space_desc {
     int32_t heads, vdim, state, groups, conv, norm_groups;
 } b200_state_space_desc;
+typedef struct b200_gated_linear_desc {
+    int32_t heads, dim, vdim;
+} b200_gated_linear_desc;
+typedef struct b200_gated_unit_desc {
+    int32_t width;
+} b200_gated_unit_desc;
 typedef struct b200_layer_desc {
     int32_t mixer;                   /* B200_MIX_* */
     b200_window_attn_desc attn;      /* WINDOW_MEMORY */
@@ -377,6 +415,10 @@ typedef struct b200_layer_desc {
     b200_moe_desc moe;               /* B200_FF_MOE */
     b200_latent_attn_desc latent;    /* LATENT_ATTN */
     b200_state_space_desc ssd;       /* STATE_SPACE */
+    int32_t rec_kind, combine;       /* ATTN_RECURRENT: B200_REC_*, B200_COMBINE_* (left branch: sattn; weights: attn_scale, mem_scale) */
+    b200_gated_linear_desc glin;     /* ATTN_RECURRENT with B200_REC_GATED_LINEAR */
+    b200_gated_unit_desc gunit;      /* ATTN_RECURRENT with B200_REC_GATED_UNIT */
+    float ff_limit, ff_slope;        /* B200_FF_CLAMPED_GLU */
 } b200_layer_desc;
 typedef struct b200_program_desc {
     int32_t width, vocab, n_layers;
@@ -391,6 +433,7 @@ typedef struct b200_program_desc {
     int32_t norm_kind;                          /* B200_NORM_* of the layer norms and the final norm */
     int32_t streams;                            /* 0: one residual stream in the forms above; >= 1: that many copies (see "streams") */
     float residual_mult;                        /* streams >= 1: factor on every sublayer's output */
+    int32_t parallel_ff;                        /* 1 = one norm per layer, the feed-forward reads the mixer's input (see "parallel_ff") */
 } b200_program_desc;
 B200_API int b200_ctx_create_layers(const b200_program_desc* prog, const b200_layer_desc* layers, int device, b200_ctx** out);
 /* One batch of token runs: run i continues sequence slot seqs[i] with lens[i] tokens (concatenated in `tokens`).  want_rows are

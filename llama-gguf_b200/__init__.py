@@ -110,13 +110,15 @@ class SoftmaxAttnDesc(C.Structure):
     _fields_ = [("heads", C.c_int32), ("kv_heads", C.c_int32), ("dim", C.c_int32), ("vdim", C.c_int32), ("mask", C.c_int32),
                 ("mask_size", C.c_int32), ("scale", C.c_float), ("qkv_bias", C.c_int32), ("conv", C.c_int32), ("qk_norm", C.c_int32),
                 ("rot_dims", C.c_int32), ("rot_base", C.c_float), ("softcap", C.c_float), ("dist_bias_exp", C.c_float),
-                ("v_mix", C.c_int32), ("out_gate", C.c_int32)]
+                ("v_mix", C.c_int32), ("out_gate", C.c_int32), ("yarn_factor", C.c_float), ("yarn_original", C.c_float),
+                ("yarn_fast", C.c_float), ("yarn_slow", C.c_float), ("rot_after_norm", C.c_int32), ("v_rot_base", C.c_float),
+                ("sink", C.c_int32), ("o_bias", C.c_int32)]
 
 
 class MoeDesc(C.Structure):
     """b200_moe_desc"""
     _fields_ = [("experts", C.c_int32), ("top", C.c_int32), ("expert_ff", C.c_int32), ("shared_ff", C.c_int32), ("act", C.c_int32),
-                ("route", C.c_int32), ("route_scale", C.c_float)]
+                ("route", C.c_int32), ("route_scale", C.c_float), ("weight_input", C.c_int32)]
 
 
 class RotaryDesc(C.Structure):
@@ -138,11 +140,23 @@ class StateSpaceDesc(C.Structure):
                 ("norm_groups", C.c_int32)]
 
 
+class GatedLinearDesc(C.Structure):
+    """b200_gated_linear_desc"""
+    _fields_ = [("heads", C.c_int32), ("dim", C.c_int32), ("vdim", C.c_int32)]
+
+
+class GatedUnitDesc(C.Structure):
+    """b200_gated_unit_desc"""
+    _fields_ = [("width", C.c_int32)]
+
+
 class LayerDesc(C.Structure):
     """b200_layer_desc"""
     _fields_ = [("mixer", C.c_int32), ("attn", WindowAttnDesc), ("mem", MatrixMemoryDesc), ("attn_scale", C.c_float),
                 ("mem_scale", C.c_float), ("delta", GatedDeltaDesc), ("ff", C.c_int32), ("sattn", SoftmaxAttnDesc),
-                ("ff_kind", C.c_int32), ("moe", MoeDesc), ("latent", LatentAttnDesc), ("ssd", StateSpaceDesc)]
+                ("ff_kind", C.c_int32), ("moe", MoeDesc), ("latent", LatentAttnDesc), ("ssd", StateSpaceDesc),
+                ("rec_kind", C.c_int32), ("combine", C.c_int32), ("glin", GatedLinearDesc), ("gunit", GatedUnitDesc),
+                ("ff_limit", C.c_float), ("ff_slope", C.c_float)]
 
 
 class ProgramDesc(C.Structure):
@@ -151,18 +165,21 @@ class ProgramDesc(C.Structure):
                 ("max_batch", C.c_int32), ("norm_eps", C.c_float), ("embed_scale", C.c_float), ("logit_scale", C.c_float),
                 ("pos_sinusoid", C.c_int32), ("loop_start", C.c_int32), ("loop_stop", C.c_int32), ("loop_times", C.c_int32),
                 ("compute", C.c_int32), ("post_norm", C.c_int32), ("residual_alpha", C.c_float), ("norm_weight_offset", C.c_float),
-                ("norm_kind", C.c_int32), ("streams", C.c_int32), ("residual_mult", C.c_float)]
+                ("norm_kind", C.c_int32), ("streams", C.c_int32), ("residual_mult", C.c_float), ("parallel_ff", C.c_int32)]
 
 
-MIX_WINDOW_MEMORY, MIX_GATED_DELTA, MIX_SOFTMAX_ATTN, MIX_LATENT_ATTN, MIX_STATE_SPACE = 1, 2, 3, 4, 5
+MIX_WINDOW_MEMORY, MIX_GATED_DELTA, MIX_SOFTMAX_ATTN, MIX_LATENT_ATTN, MIX_STATE_SPACE, MIX_ATTN_RECURRENT = 1, 2, 3, 4, 5, 6
 NORM_RMS, NORM_LAYER = 0, 1
-ACT_RELU2, ACT_GELU = 0, 1
-ROUTE_TOP_SOFTMAX, ROUTE_SOFTMAX_TOP = 0, 1
-MASK_WINDOW, MASK_CHUNK = 0, 1
+ACT_RELU2, ACT_GELU, ACT_SILU_GLU = 0, 1, 2
+ROUTE_TOP_SOFTMAX, ROUTE_SOFTMAX_TOP, ROUTE_SIGMOID_TOP = 0, 1, 2
+MASK_WINDOW, MASK_CHUNK, MASK_CAUSAL = 0, 1, 2
+SINK_NONE, SINK_LEARNED, SINK_ZERO = 0, 1, 2
+REC_GATED_LINEAR, REC_GATED_UNIT = 1, 2
+COMBINE_WEIGHTED, COMBINE_NORMED_MEAN = 0, 1
 QKNORM_NONE, QKNORM_HEAD_WEIGHT, QKNORM_WHOLE_WEIGHT, QKNORM_HEAD_UNIT = 0, 1, 2, 3
 GATE_NONE, GATE_CHANNEL, GATE_HEAD = 0, 1, 2
 VMIX_NONE, VMIX_SOURCE, VMIX_BLEND = 0, 1, 2
-FF_RELU2, FF_GATED_GELU, FF_MOE = 0, 1, 2
+FF_RELU2, FF_GATED_GELU, FF_MOE, FF_CLAMPED_GLU = 0, 1, 2, 3
 COMPUTE_BF16, COMPUTE_F32 = 0, 1
 BF16 = 30   # ggml's id; layer-program contexts only
 

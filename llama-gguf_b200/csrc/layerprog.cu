@@ -131,7 +131,8 @@ __global__ void lp_rmsnorm_kernel(float* __restrict__ x, const float* __restrict
 }
 
 // ------------------------------------------------------------------------------------------------ GEMM (CUDA cores)
-// Y[r][n] = epi(alpha * sum_k X[r][k] * W[n][k]); products of the stored operand values in f32, f32 accumulation.
+// Y[r][n] = epi(alpha * sum_k X[r][k] * W[n][k] + bias[n]); products of the stored operand values in f32, f32 accumulation
+// (bias: f32 per output column, or null).
 enum { EPI_STORE = 0, EPI_ADD = 1, EPI_RELU2 = 2, EPI_GELU = 3, EPI_COUNT = 4 };
 __device__ __forceinline__ float gelu_erf_f(float z) { return 0.5f * z * (1.0f + erff(z * 0.7071067811865476f)); }
 template <typename T, int EPI>
@@ -157,7 +158,8 @@ struct ZStride {
 constexpr int GB = 64, GK = 16;
 template <typename T, int EPI>
 __global__ void __launch_bounds__(256) lp_gemm_kernel(const T* __restrict__ X, int ldx, const T* __restrict__ W, int ldw, void* __restrict__ Y,
-                                                      int ldy, int R, int N, int K, float alpha, const int* __restrict__ seg, size_t w_zstride, ZStride zs) {
+                                                      int ldy, int R, int N, int K, float alpha, const int* __restrict__ seg, size_t w_zstride, ZStride zs,
+                                                      const float* __restrict__ bias) {
     __shared__ float As[GK][GB + 4];
     __shared__ float Bs[GK][GB + 4];
     if (!seg && gridDim.z > 1) {
@@ -206,7 +208,7 @@ __global__ void __launch_bounds__(256) lp_gemm_kernel(const T* __restrict__ X, i
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             const int n = n0 + tx * 4 + j;
-            if (n < N) epi_store<T, EPI>(Y, (size_t)r * ldy + n, alpha * acc[i][j]);
+            if (n < N) epi_store<T, EPI>(Y, (size_t)r * ldy + n, alpha * acc[i][j] + (bias ? bias[n] : 0.0f));
         }
     }
 }
@@ -253,7 +255,7 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32
 template <int TN, int EPI>
 __global__ void __launch_bounds__(128) lp_gemm_tc_kernel(const bf16* __restrict__ X, int ldx, const bf16* __restrict__ W, int ldw,
                                                          void* __restrict__ Y, int ldy, int R, int N, int K, float alpha, int* err,
-                                                         const int* __restrict__ seg, size_t w_zstride, ZStride zs) {
+                                                         const int* __restrict__ seg, size_t w_zstride, ZStride zs, const float* __restrict__ bias) {
     extern __shared__ __align__(1024) uint8_t tc_smem[];
     if (!seg && gridDim.z > 1) {
         W += blockIdx.z * w_zstride;
@@ -356,6 +358,7 @@ __global__ void __launch_bounds__(128) lp_gemm_tc_kernel(const bf16* __restrict_
     }
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const int n = n0 + tid;
+    const float bn = (bias && n < N) ? bias[n] : 0.0f;
     if (alive) {
 #pragma unroll 1
         for (int c0 = 0; c0 < TN; c0 += 32) {
@@ -375,7 +378,7 @@ __global__ void __launch_bounds__(128) lp_gemm_tc_kernel(const bf16* __restrict_
 #pragma unroll
                 for (int c = 0; c < 32; c++) {
                     const int t = t0 + c0 + c;
-                    if (t < R) epi_store<bf16, EPI>(Y, (size_t)t * ldy + n, alpha * __uint_as_float(v[c]));
+                    if (t < R) epi_store<bf16, EPI>(Y, (size_t)t * ldy + n, alpha * __uint_as_float(v[c]) + bn);
                 }
             }
         }
@@ -413,7 +416,7 @@ template <> struct Vec8<float> {
 template <typename T, int EPI>
 __global__ void __launch_bounds__(256) lp_gemv_kernel(const T* __restrict__ X, int ldx, const T* __restrict__ W, int ldw, void* __restrict__ Y,
                                                       int ldy, int R, int N, int K, float alpha, int vec_ok, int stage, RowsTail tail, int nh,
-                                                      ZStride zs) {
+                                                      ZStride zs, const float* __restrict__ bias) {
     // nh > 0: the N outputs are heads of nh columns; head z = n / nh reads X `zs.x` elements on and writes column z * zs.y + n % nh
     extern __shared__ __align__(16) uint8_t gv_smem[];
     const T* X0 = X;
@@ -467,7 +470,7 @@ __global__ void __launch_bounds__(256) lp_gemv_kernel(const T* __restrict__ X, i
         for (int i = 0; i < GV_ROWS; i++) {
             if (i < nr) {
                 const float s = wsum(acc[i]);
-                if (lane == 0) epi_store<T, EPI>(Y, (size_t)(rb + i) * ldy + ycol, alpha * s);
+                if (lane == 0) epi_store<T, EPI>(Y, (size_t)(rb + i) * ldy + ycol, alpha * s + (bias ? bias[n] : 0.0f));
             }
         }
     }
@@ -481,7 +484,7 @@ __global__ void __launch_bounds__(256) lp_gemv_kernel(const T* __restrict__ X, i
 template <typename T, int EPI>
 __global__ void __launch_bounds__(256) lp_gemv_norm_kernel(const float* __restrict__ X, const int* __restrict__ gather, const float* __restrict__ nw,
                                                            float eps, const T* __restrict__ W, void* __restrict__ Y, int ldy, int R, int N, int K,
-                                                           float alpha, int center) {
+                                                           float alpha, int center, T* __restrict__ hn_out) {
     extern __shared__ __align__(16) uint8_t gn_smem[];
     T* xs = reinterpret_cast<T*>(gn_smem);            // [R][K]
     __shared__ float red[8];
@@ -518,7 +521,11 @@ __global__ void __launch_bounds__(256) lp_gemv_norm_kernel(const float* __restri
         }
         __syncthreads();
         const float inv = inv_s;
-        for (int k = threadIdx.x; k < K; k += 256) xs[(size_t)r * K + k] = from_f<T>((xr[k] - mean) * inv * nw[k]);
+        for (int k = threadIdx.x; k < K; k += 256) {
+            const T v = from_f<T>((xr[k] - mean) * inv * nw[k]);
+            xs[(size_t)r * K + k] = v;
+            if (hn_out && blockIdx.x == 0) hn_out[(size_t)r * K + k] = v;   // (a later kernel of the layer reads the normed rows too)
+        }
     }
     __syncthreads();
     constexpr int VN = Vec8<T>::N;
@@ -568,7 +575,23 @@ struct AttnGeom {
     float softcap;                    // > 0: score <- softcap tanh(score / softcap)
     float slope_exp;                  // > 0: score -= 2^(-slope_exp (h + 1) / H) (i - j)
     int v_in_k;                       // 1: there are no value rows; a value is the first vdim entries of its (single, G = 1) key row
+    int sink_mode;                    // B200_SINK_*: one more term exp(c) in the softmax's denominator, without key or value
+    const float* sink;                // [H]: c per head (B200_SINK_LEARNED)
+    const float* vrot;                // [rows][vdim]: cos | sin of the angles that turn a row's summed values back, or null
 };
+// the extra term of the denominator as the start of the running (maximum, sum): a key with score c and no value
+__device__ __forceinline__ bool attn_sink(const AttnGeom& a, int h, float* c) {
+    if (a.sink_mode == B200_SINK_NONE) return false;
+    *c = a.sink_mode == B200_SINK_LEARNED ? a.sink[h] : 0.0f;
+    return true;
+}
+// pair (2m, 2m + 1) of a head's summed values turned by minus the row's angle: tab = cos [vdim / 2] | sin [vdim / 2]
+__device__ __forceinline__ void attn_turn_back(const float* tab, int half, int m, float& u, float& v) {
+    const float c = tab[m], s = tab[half + m];
+    const float nu = u * c + v * s, nv = v * c - u * s;
+    u = nu;
+    v = nv;
+}
 // out_gate: 0 none, 1 = sigmoid of a gate column per value channel, 2 = one gate column per head
 __device__ __forceinline__ float attn_gate(const AttnGeom& a, const float* gate_row, int h, int ch) {
     return a.out_gate == 1 ? sigmoid_f(gate_row[h * a.vdim + ch]) : a.out_gate == 2 ? sigmoid_f(gate_row[h]) : 1.0f;
@@ -620,6 +643,7 @@ __global__ void __launch_bounds__(32 * ATT_WARPS) lp_window_attn_kernel(StepMeta
     float* qs = smem;                                  // [dim]
     float* acc_s = smem + ((a.dim + 3) & ~3);          // [ATT_WARPS][vdim]
     float* ml_s = acc_s + ATT_WARPS * a.vdim;          // [ATT_WARPS][2]
+    float* om = ml_s + 2 * ATT_WARPS;                  // [vdim] (with vrot only)
     const int r = blockIdx.x, h = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int run = sm.row_run[r], i = sm.row_pos[r];
     const int g = h * a.G / a.H;
@@ -658,6 +682,10 @@ __global__ void __launch_bounds__(32 * ATT_WARPS) lp_window_attn_kernel(StepMeta
     const int nb0 = (a_end + 31) >> 5, nb1 = (i + 1 - lo + 31) >> 5;
     const float slope = attn_slope(a, h);
     float m = -INFINITY, l = 0.0f;
+    {
+        float c;
+        if (warp == 0 && attn_sink(a, h, &c)) { m = c; l = 1.0f; }
+    }
     float acc[VCH];
 #pragma unroll
     for (int c = 0; c < VCH; c++) acc[c] = 0.0f;
@@ -760,6 +788,23 @@ __global__ void __launch_bounds__(32 * ATT_WARPS) lp_window_attn_kernel(StepMeta
     }
     const float invl = 1.0f / lsum;
     const float* gate = P + (size_t)r * ldp + a.g_off;
+    if (a.vrot) {   // the merged sums first, then every pair is turned back by the row's angle
+        for (int ch = threadIdx.x; ch < a.vdim; ch += blockDim.x) {
+            float o = 0.0f;
+#pragma unroll
+            for (int w = 0; w < ATT_WARPS; w++) o = fmaf(acc_s[w * a.vdim + ch], wgt[w], o);
+            om[ch] = o * invl;
+        }
+        __syncthreads();
+        const float* tab = a.vrot + (size_t)r * a.vdim;
+        for (int pm = threadIdx.x; pm < a.vdim / 2; pm += blockDim.x) {
+            float u = om[2 * pm], v = om[2 * pm + 1];
+            attn_turn_back(tab, a.vdim / 2, pm, u, v);
+            out[(size_t)r * a.out_ld + h * a.vdim + 2 * pm] = from_f<OutT>(u * attn_gate(a, gate, h, 2 * pm) * a.out_scale);
+            out[(size_t)r * a.out_ld + h * a.vdim + 2 * pm + 1] = from_f<OutT>(v * attn_gate(a, gate, h, 2 * pm + 1) * a.out_scale);
+        }
+        return;
+    }
     for (int ch = threadIdx.x; ch < a.vdim; ch += blockDim.x) {
         float o = 0.0f;
 #pragma unroll
@@ -821,6 +866,10 @@ __global__ void __launch_bounds__(128) lp_window_attn_tile_kernel(StepMeta sm, A
 #pragma unroll
     for (int n = 0; n < DV / 8; n++) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;
+    {
+        float c;
+        if (attn_sink(a, h, &c)) { m0 = m1 = c; l0 = l1 = 1.0f; }
+    }
     const int first = p0 + t0, last = p0 + min(t0 + AT_Q, len) - 1;
     const int lo0 = attn_lo(a, first);
     const int a_end = min(a.keep_first, lo0);
@@ -960,11 +1009,15 @@ __global__ void __launch_bounds__(128) lp_window_attn_tile_kernel(StepMeta sm, A
         if (ch < a.vdim) {
             if (ok0) {
                 const float g0 = attn_gate(a, gate0, h, ch), g1 = attn_gate(a, gate0, h, ch + 1);
-                *reinterpret_cast<uint32_t*>(out0 + ch) = pack_bf2(o[n][0] * inv0 * g0, o[n][1] * inv0 * g1);
+                float u = o[n][0] * inv0, v = o[n][1] * inv0;
+                if (a.vrot) attn_turn_back(a.vrot + (size_t)(r0 + tq0) * a.vdim, a.vdim / 2, ch >> 1, u, v);
+                *reinterpret_cast<uint32_t*>(out0 + ch) = pack_bf2(u * g0, v * g1);
             }
             if (ok1) {
                 const float g0 = attn_gate(a, gate1, h, ch), g1 = attn_gate(a, gate1, h, ch + 1);
-                *reinterpret_cast<uint32_t*>(out1 + ch) = pack_bf2(o[n][2] * inv1 * g0, o[n][3] * inv1 * g1);
+                float u = o[n][2] * inv1, v = o[n][3] * inv1;
+                if (a.vrot) attn_turn_back(a.vrot + (size_t)(r0 + tq1) * a.vdim, a.vdim / 2, ch >> 1, u, v);
+                *reinterpret_cast<uint32_t*>(out1 + ch) = pack_bf2(u * g0, v * g1);
             }
         }
     }
@@ -1244,8 +1297,8 @@ __global__ void __launch_bounds__(SCAN_BD) lp_gated_delta_kernel(StepMeta sm, De
         }
 }
 
-// out[r][h][c] = o / sqrt(mean_c o^2 + eps) * w[w_per_head ? c : h * vdim + c] * act(gate), act = sigmoid (0) or SiLU (1); one warp
-// per (row, head).  The result is the input of the mixer's output projection.
+// out[r][h][c] = o / sqrt(mean_c o^2 + eps) * w[w_per_head ? c : h * vdim + c] * act(gate), act = sigmoid (0), SiLU (1) or no gate at
+// all (2); one warp per (row, head).  The result is the input of the mixer's output projection.
 template <typename OutT>
 __global__ void lp_headnorm_gate_kernel(const float* __restrict__ O, int ldo, const float* __restrict__ P, int ldp, int g_off,
                                         const float* __restrict__ w, int w_per_head, int H, int vdim, float eps, int act,
@@ -1260,8 +1313,8 @@ __global__ void lp_headnorm_gate_kernel(const float* __restrict__ O, int ldo, co
     const float inv = 1.0f / sqrtf(ss / (float)vdim + eps);
     const float* gate = P + (size_t)r * ldp + g_off + h * vdim;
     for (int c = lane; c < vdim; c += 32) {
-        const float z = gate[c];
-        const float ga = act ? z * sigmoid_f(z) : sigmoid_f(z);
+        const float z = act == 2 ? 0.0f : gate[c];
+        const float ga = act == 2 ? 1.0f : act ? z * sigmoid_f(z) : sigmoid_f(z);
         out[(size_t)r * out_ld + h * vdim + c] = from_f<OutT>(o[c] * inv * w[w_per_head ? c : h * vdim + c] * ga * out_scale);
     }
 }
@@ -1294,6 +1347,7 @@ __global__ void lp_argmax_kernel(const float* __restrict__ logits, int vocab, in
 #include "lp_streams.cuh"
 #include "lp_latent_attn.cuh"
 #include "lp_state_space.cuh"
+#include "lp_gated_recurrent.cuh"
 
 // out [H][b][a] = in [H][a][b]: a mixer's per-head matrices turned once at load
 template <typename T>
@@ -1346,6 +1400,19 @@ struct LayerPlan {
     // state-space mixer
     SsdGeom sg{};
     const float *conv_b = nullptr, *ssd_D = nullptr, *ssd_norm = nullptr;
+    // softmax mixer options: the extra term of the denominator per head, the output projection's bias, the values' own frequencies
+    const float *sink = nullptr, *o_bias = nullptr;
+    const double* v_freq = nullptr;
+    // attention beside a recurrent unit: the unit's geometry and vectors, the right branch's own output projection and the two
+    // branch norms (B200_COMBINE_NORMED_MEAN), the operand widths of the two branches
+    GlinGeom gl{};
+    GunitGeom gu{};
+    const float *rec_b0 = nullptr, *rec_b1 = nullptr, *rec_lower = nullptr, *rec_norm = nullptr, *left_out = nullptr, *right_out = nullptr;
+    void* wo_right = nullptr;
+    int k_left = 0, k_right = 0;
+    // parallel_ff: first column of the feed-forward's part ([gate | up], [up] or the router) in the layer's input projection
+    int ff_off = -1;
+    int up_router_rows = 0;      // rows of the router at the head of w_up (0 when the router sits in the layer's input projection)
     // multi-stream layer form: [in | out | mix] of the two sublayers (null: identity)
     const float *hc_in[2] = {nullptr, nullptr}, *hc_out[2] = {nullptr, nullptr}, *hc_mix[2] = {nullptr, nullptr};
 };
@@ -1386,6 +1453,9 @@ struct LpModel {
     void* moe_xp = nullptr;             // the tokens' rows gathered in expert order, compute type
     float* moe_yp = nullptr;            // the experts' outputs in the same order
     int max_vsrc = 0, max_experts = 0, max_top = 0;
+    float* vrot = nullptr;              // [rows][max_vrot]: cos | sin of the angles that turn a row's summed values back
+    int max_vrot = 0;
+    bool need_y2 = false;               // m->y holds two sublayer outputs per row (branches that are normed before they are summed)
     void *hn = nullptr, *act_a = nullptr, *hw = nullptr;
     int* pick = nullptr;
     float* h_logits = nullptr;          // pinned
@@ -1469,7 +1539,7 @@ bool is_matrix_name(const std::string& n) {
     // vectors) is kept in f32
     if (n == "embed" || n == "head") return true;
     static const char* suf[] = {".q", ".k", ".v", ".g", ".o", ".i", ".f", ".a", ".b", ".up", ".down", ".gate", ".router",
-                                ".dq", ".uq", ".dkv", ".uk", ".uv", ".in"};
+                                ".dq", ".uq", ".dkv", ".uk", ".uv", ".in", ".z", ".x"};
     for (const char* s : suf) {
         const size_t L = strlen(s);
         if (n.size() > L && n.compare(n.size() - L, L, s) == 0) return true;
@@ -1491,7 +1561,7 @@ void launch(LpModel* m, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t sm
 // The tensor-core GEMM takes bf16 operands whose rows are 16-byte aligned (K and the row pitches multiples of 8).
 template <int TN>
 bool tc_launch(LpModel* m, const bf16* x, int ldx, const bf16* w, int ldw, int N, int K, void* Y, int ldy, int R, float alpha, int epi, const int* seg,
-               int groups, size_t wz, ZStride zs) {
+               int groups, size_t wz, ZStride zs, const float* bias) {
     const size_t smem = (size_t)TC_STAGES * (TC_M + TN) * 128 + 1024;
     static bool once[EPI_COUNT][64] = {};
     int dev = 0;
@@ -1509,7 +1579,7 @@ bool tc_launch(LpModel* m, const bf16* x, int ldx, const bf16* w, int ldw, int N
 #define LP_TC(E)                                                                                                                       \
     do {                                                                                                                               \
         if (!prep(lp_gemm_tc_kernel<TN, E>, E)) return false;                                                                          \
-        launch(m, lp_gemm_tc_kernel<TN, E>, grid, block, smem, x, ldx, w, ldw, Y, ldy, R, N, K, alpha, m->tc_err, seg, wz, zs);        \
+        launch(m, lp_gemm_tc_kernel<TN, E>, grid, block, smem, x, ldx, w, ldw, Y, ldy, R, N, K, alpha, m->tc_err, seg, wz, zs, bias);  \
     } while (0)
     if (epi == EPI_STORE) LP_TC(EPI_STORE);
     else if (epi == EPI_ADD) LP_TC(EPI_ADD);
@@ -1519,14 +1589,14 @@ bool tc_launch(LpModel* m, const bf16* x, int ldx, const bf16* w, int ldw, int N
     return true;
 }
 bool tc_gemm(LpModel* m, const void* X, int ldx, const void* W, int ldw, int N, int K, void* Y, int ldy, int R, float alpha, int epi, const int* seg,
-             int groups, size_t wz, ZStride zs) {
+             int groups, size_t wz, ZStride zs, const float* bias) {
     if (m->f32 || !m->use_tc || R < m->tc_min_rows) return false;
     if (K % 8 || ldx % 8 || ldw % 8 || wz % 8 || zs.x % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return false;
     const bf16* x = (const bf16*)X;
     const bf16* w = (const bf16*)W;
-    if (R <= 64) return tc_launch<64>(m, x, ldx, w, ldw, N, K, Y, ldy, R, alpha, epi, seg, groups, wz, zs);
-    if (R <= 128) return tc_launch<128>(m, x, ldx, w, ldw, N, K, Y, ldy, R, alpha, epi, seg, groups, wz, zs);   // (wider token tiles move fewer operand bytes per FLOP: measured 2.5x on a 2048 x 8192 x 2048 product even at 128 CTAs)
-    return tc_launch<256>(m, x, ldx, w, ldw, N, K, Y, ldy, R, alpha, epi, seg, groups, wz, zs);
+    if (R <= 64) return tc_launch<64>(m, x, ldx, w, ldw, N, K, Y, ldy, R, alpha, epi, seg, groups, wz, zs, bias);
+    if (R <= 128) return tc_launch<128>(m, x, ldx, w, ldw, N, K, Y, ldy, R, alpha, epi, seg, groups, wz, zs, bias);   // (wider token tiles move fewer operand bytes per FLOP: measured 2.5x on a 2048 x 8192 x 2048 product even at 128 CTAs)
+    return tc_launch<256>(m, x, ldx, w, ldw, N, K, Y, ldy, R, alpha, epi, seg, groups, wz, zs, bias);
 }
 
 // Y = epi(alpha X W^T): rows of the step against a [N][K] matrix in the compute type.  Without `seg`, groups > 1 batches the product
@@ -1534,7 +1604,7 @@ bool tc_gemm(LpModel* m, const void* X, int ldx, const void* W, int ldw, int N, 
 // [z zs.y, z zs.y + N) of Y.
 template <typename T>
 void gemm_t(LpModel* m, const void* X, int ldx, const void* W, int ldw, int N, int K, void* Y, int ldy, int R, float alpha, int epi, const int* seg = nullptr,
-            int groups = 1, size_t wz = 0, const RowsTail* tail = nullptr, ZStride zs = ZStride{0, 0}) {
+            int groups = 1, size_t wz = 0, const RowsTail* tail = nullptr, ZStride zs = ZStride{0, 0}, const float* bias = nullptr) {
     const T* x = (const T*)X;
     const T* w = (const T*)W;
     if (R <= 2 * GV_ROWS && !seg) {
@@ -1549,7 +1619,7 @@ void gemm_t(LpModel* m, const void* X, int ldx, const void* W, int ldw, int N, i
         const size_t smem = stage ? xbytes : 0;
         const RowsTail tl = tail ? *tail : RowsTail{};
         const int nh = heads ? N : 0;
-#define LP_GV(E) launch(m, lp_gemv_kernel<T, E>, grid, block, smem, x, ldx, w, ldw, Y, ldy, R, Nall, K, alpha, vec_ok, stage, tl, nh, zs)
+#define LP_GV(E) launch(m, lp_gemv_kernel<T, E>, grid, block, smem, x, ldx, w, ldw, Y, ldy, R, Nall, K, alpha, vec_ok, stage, tl, nh, zs, bias)
         if (epi == EPI_STORE) LP_GV(EPI_STORE);
         else if (epi == EPI_ADD) LP_GV(EPI_ADD);
         else if (epi == EPI_GELU) LP_GV(EPI_GELU);
@@ -1557,9 +1627,9 @@ void gemm_t(LpModel* m, const void* X, int ldx, const void* W, int ldw, int N, i
 #undef LP_GV
         return;
     }
-    if (tc_gemm(m, X, ldx, W, ldw, N, K, Y, ldy, R, alpha, epi, seg, groups, wz, zs)) return;
+    if (tc_gemm(m, X, ldx, W, ldw, N, K, Y, ldy, R, alpha, epi, seg, groups, wz, zs, bias)) return;
     dim3 grid((N + GB - 1) / GB, (R + GB - 1) / GB, groups), block(256);
-#define LP_GM(E) launch(m, lp_gemm_kernel<T, E>, grid, block, 0, x, ldx, w, ldw, Y, ldy, R, N, K, alpha, seg, wz, zs)
+#define LP_GM(E) launch(m, lp_gemm_kernel<T, E>, grid, block, 0, x, ldx, w, ldw, Y, ldy, R, N, K, alpha, seg, wz, zs, bias)
     if (epi == EPI_STORE) LP_GM(EPI_STORE);
     else if (epi == EPI_ADD) LP_GM(EPI_ADD);
     else if (epi == EPI_GELU) LP_GM(EPI_GELU);
@@ -1567,9 +1637,10 @@ void gemm_t(LpModel* m, const void* X, int ldx, const void* W, int ldw, int N, i
 #undef LP_GM
 }
 // tail: few rows only (the caller has checked R): the last block goes on with rows_tail
-void gemm(LpModel* m, const void* X, int ldx, const void* W, int N, int K, void* Y, int ldy, int R, float alpha, int epi, const RowsTail* tail = nullptr) {
-    if (m->f32) gemm_t<float>(m, X, ldx, W, K, N, K, Y, ldy, R, alpha, epi, nullptr, 1, 0, tail);
-    else gemm_t<bf16>(m, X, ldx, W, K, N, K, Y, ldy, R, alpha, epi, nullptr, 1, 0, tail);
+void gemm(LpModel* m, const void* X, int ldx, const void* W, int N, int K, void* Y, int ldy, int R, float alpha, int epi, const RowsTail* tail = nullptr,
+          const float* bias = nullptr) {
+    if (m->f32) gemm_t<float>(m, X, ldx, W, K, N, K, Y, ldy, R, alpha, epi, nullptr, 1, 0, tail, ZStride{0, 0}, bias);
+    else gemm_t<bf16>(m, X, ldx, W, K, N, K, Y, ldy, R, alpha, epi, nullptr, 1, 0, tail, ZStride{0, 0}, bias);
 }
 // `groups` products in one launch (grid.z): group g multiplies rows [seg[2g], seg[2g] + seg[2g + 1]) of X -- the counts live on the
 // device, R is their upper bound -- with the matrix at Wm + g * zs elements, whose rows are ldw apart (contiguous matrices: ldw = K,
@@ -1585,9 +1656,9 @@ void gemm_heads(LpModel* m, const void* X, int ldx, size_t xz, const void* Wm, i
     else gemm_t<bf16>(m, X, ldx, Wm, K, N, K, Y, ldy, R, 1.0f, EPI_STORE, nullptr, heads, (size_t)N * K, nullptr, ZStride{xz, yz});
 }
 // One product with a weight matrix whose rows are `ldw` apart (a block of columns of a wider matrix).
-void gemm_ld(LpModel* m, const void* X, int ldx, const void* Wm, int ldw, int N, int K, void* Y, int ldy, int R, int epi) {
-    if (m->f32) gemm_t<float>(m, X, ldx, Wm, ldw, N, K, Y, ldy, R, 1.0f, epi);
-    else gemm_t<bf16>(m, X, ldx, Wm, ldw, N, K, Y, ldy, R, 1.0f, epi);
+void gemm_ld(LpModel* m, const void* X, int ldx, const void* Wm, int ldw, int N, int K, void* Y, int ldy, int R, int epi, const float* bias = nullptr) {
+    if (m->f32) gemm_t<float>(m, X, ldx, Wm, ldw, N, K, Y, ldy, R, 1.0f, epi, nullptr, 1, 0, nullptr, ZStride{0, 0}, bias);
+    else gemm_t<bf16>(m, X, ldx, Wm, ldw, N, K, Y, ldy, R, 1.0f, epi, nullptr, 1, 0, nullptr, ZStride{0, 0}, bias);
 }
 
 int norm_center(const LpModel* m) { return m->p.norm_kind == B200_NORM_LAYER ? 1 : 0; }
@@ -1602,7 +1673,7 @@ void rmsnorm(LpModel* m, float* x, const float* add, const float* w, void* out, 
 // written back into the stream).
 template <typename T>
 bool gemv_norm_t(LpModel* m, const float* x, const int* gather, const float* nw, const void* W, int N, int K, void* Y, int ldy, int R, float alpha,
-                 int epi) {
+                 int epi, void* hn_out) {
     constexpr int VN = Vec8<T>::N;
     const size_t smem = (size_t)R * K * sizeof(T);
     if (R > 2 * GV_ROWS || K % VN || ((uintptr_t)W & 15) || smem > 96 * 1024) return false;
@@ -1622,18 +1693,20 @@ bool gemv_norm_t(LpModel* m, const float* x, const int* gather, const float* nw,
     const T* w = (const T*)W;
     if (epi == EPI_STORE) {
         if (!prep(lp_gemv_norm_kernel<T, EPI_STORE>, 0)) return false;
-        launch(m, lp_gemv_norm_kernel<T, EPI_STORE>, grid, block, smem, x, gather, nw, m->p.norm_eps, w, Y, ldy, R, N, K, alpha, norm_center(m));
+        launch(m, lp_gemv_norm_kernel<T, EPI_STORE>, grid, block, smem, x, gather, nw, m->p.norm_eps, w, Y, ldy, R, N, K, alpha, norm_center(m), (T*)hn_out);
     } else if (epi == EPI_RELU2) {
         if (!prep(lp_gemv_norm_kernel<T, EPI_RELU2>, 2)) return false;
-        launch(m, lp_gemv_norm_kernel<T, EPI_RELU2>, grid, block, smem, x, gather, nw, m->p.norm_eps, w, Y, ldy, R, N, K, alpha, norm_center(m));
+        launch(m, lp_gemv_norm_kernel<T, EPI_RELU2>, grid, block, smem, x, gather, nw, m->p.norm_eps, w, Y, ldy, R, N, K, alpha, norm_center(m), (T*)hn_out);
     } else return false;
     return true;
 }
+// keep: the normed rows are also wanted in `scratch` afterwards (the fused kernel then writes them out as well)
 void norm_gemm(LpModel* m, float* x, const float* add, const int* gather, const float* nw, void* scratch, const void* W, int N, void* Y, int ldy,
-               int R, float alpha, int epi) {
+               int R, float alpha, int epi, bool keep = false) {
     const int K = m->p.width;
     if (!add && m->use_fuse) {
-        if (m->f32 ? gemv_norm_t<float>(m, x, gather, nw, W, N, K, Y, ldy, R, alpha, epi) : gemv_norm_t<bf16>(m, x, gather, nw, W, N, K, Y, ldy, R, alpha, epi))
+        void* hn_out = keep ? scratch : nullptr;
+        if (m->f32 ? gemv_norm_t<float>(m, x, gather, nw, W, N, K, Y, ldy, R, alpha, epi, hn_out) : gemv_norm_t<bf16>(m, x, gather, nw, W, N, K, Y, ldy, R, alpha, epi, hn_out))
             return;
     }
     rmsnorm(m, x, add, nw, scratch, gather, R);
@@ -1658,6 +1731,7 @@ int lp_create(const b200_program_desc* prog, const b200_layer_desc* layers, int 
     if (p.norm_kind == B200_NORM_LAYER && p.post_norm) return bad("the layer norm is not available in the norm-after-sum form");
     if (p.streams < 0 || p.streams > ST_MAX) return bad("streams must be 0 .. " + std::to_string(ST_MAX));
     if (p.streams > 0 && (p.post_norm || looped)) return bad("the multi-stream form takes neither the norm after the sum nor a repeated range");
+    if (p.parallel_ff && (p.post_norm || p.streams > 0)) return bad("parallel_ff belongs to the norm-first form with one residual stream");
     for (int i = 0; i < p.n_layers; i++) {
         const b200_layer_desc& L = layers[i];
         const std::string at = "layer " + std::to_string(i) + ": ";
@@ -1673,13 +1747,18 @@ int lp_create(const b200_program_desc* prog, const b200_layer_desc* layers, int 
             const b200_gated_delta_desc& g = L.delta;
             if (g.heads <= 0 || g.kv_heads <= 0 || g.dim <= 0 || g.vdim <= 0 || g.kv_heads > g.heads || g.conv < 1) return bad(at + "bad delta-rule sizes");
             if (g.dim > 256) return bad(at + "delta-rule key size above 256");
-        } else if (L.mixer == B200_MIX_SOFTMAX_ATTN) {
+        } else if (L.mixer == B200_MIX_SOFTMAX_ATTN || L.mixer == B200_MIX_ATTN_RECURRENT) {
             const b200_softmax_attn_desc& a = L.sattn;
             if (a.heads <= 0 || a.kv_heads <= 0 || a.dim <= 0 || a.vdim <= 0 || a.kv_heads > a.heads || a.heads % a.kv_heads)
                 return bad(at + "bad attention head counts or sizes");
-            if (a.mask_size <= 0 || (a.mask != B200_MASK_WINDOW && a.mask != B200_MASK_CHUNK)) return bad(at + "bad attention mask");
+            if (a.mask != B200_MASK_WINDOW && a.mask != B200_MASK_CHUNK && a.mask != B200_MASK_CAUSAL) return bad(at + "bad attention mask");
+            if (a.mask != B200_MASK_CAUSAL && a.mask_size <= 0) return bad(at + "bad attention mask");
             if (a.vdim > 32 * ATT_ACC) return bad(at + "attention value size above " + std::to_string(32 * ATT_ACC));
             if (a.rot_dims < 0 || a.rot_dims > a.dim || (a.rot_dims & 1) || (a.rot_dims > 0 && !(a.rot_base > 0.0f))) return bad(at + "bad rotary sizes");
+            if (a.yarn_factor < 0.0f || (a.yarn_factor > 0.0f && !(a.yarn_original > 0.0f && a.yarn_fast > 0.0f && a.yarn_slow > 0.0f && a.rot_base > 1.0f)))
+                return bad(at + "bad rotary scaling");
+            if (a.v_rot_base < 0.0f || (a.v_rot_base > 0.0f && (a.vdim & 1))) return bad(at + "turned values need an even value size and a positive base");
+            if (a.sink < B200_SINK_NONE || a.sink > B200_SINK_ZERO) return bad(at + "unknown sink kind");
             if (a.qk_norm < B200_QKNORM_NONE || a.qk_norm > B200_QKNORM_HEAD_UNIT) return bad(at + "unknown q/k norm");
             if (a.out_gate < B200_GATE_NONE || a.out_gate > B200_GATE_HEAD) return bad(at + "unknown output gate");
             if (a.v_mix < B200_VMIX_NONE || a.v_mix > B200_VMIX_BLEND) return bad(at + "unknown value mixing");
@@ -1692,6 +1771,17 @@ int lp_create(const b200_program_desc* prog, const b200_layer_desc* layers, int 
                 if (layers[src].sattn.kv_heads * layers[src].sattn.vdim != a.kv_heads * a.vdim) return bad(at + "blended values differ in size from their source");
             }
             if (looped && a.v_mix != B200_VMIX_NONE) return bad(at + "value mixing inside a program with a repeated range is not supported");
+            if (L.mixer == B200_MIX_ATTN_RECURRENT) {
+                if (a.v_mix != B200_VMIX_NONE) return bad(at + "the attention branch beside a recurrent unit takes no value mixing");
+                if (L.rec_kind == B200_REC_GATED_LINEAR) {
+                    if (L.glin.heads <= 0 || L.glin.dim <= 0 || L.glin.vdim <= 0) return bad(at + "bad gated-linear sizes");
+                    if (L.glin.dim > 256) return bad(at + "gated-linear key size above 256");
+                } else if (L.rec_kind == B200_REC_GATED_UNIT) {
+                    if (L.gunit.width <= 0) return bad(at + "bad gated-unit width");
+                } else return bad(at + "unknown recurrent unit");
+                if (L.combine != B200_COMBINE_WEIGHTED && L.combine != B200_COMBINE_NORMED_MEAN) return bad(at + "unknown way to combine the branches");
+                if (L.combine == B200_COMBINE_NORMED_MEAN && (p.post_norm || p.streams > 0)) return bad(at + "normed branches belong to the norm-first form with one residual stream");
+            }
         } else if (L.mixer == B200_MIX_LATENT_ATTN) {
             const b200_latent_attn_desc& a = L.latent;
             if (a.heads <= 0 || a.dim <= 0 || a.rot_dim < 0 || a.vdim <= 0 || a.q_rank <= 0 || a.kv_rank <= 0) return bad(at + "bad latent-attention sizes");
@@ -1717,8 +1807,12 @@ int lp_create(const b200_program_desc* prog, const b200_layer_desc* layers, int 
         if (L.ff_kind == B200_FF_MOE) {
             const b200_moe_desc& e = L.moe;
             if (e.experts <= 0 || e.top <= 0 || e.top > e.experts || e.expert_ff <= 0 || e.shared_ff < 0) return bad(at + "bad mixture-of-experts sizes");
-            if ((e.act != B200_ACT_RELU2 && e.act != B200_ACT_GELU) || (e.route != B200_ROUTE_TOP_SOFTMAX && e.route != B200_ROUTE_SOFTMAX_TOP))
+            if (e.act < B200_ACT_RELU2 || e.act > B200_ACT_SILU_GLU || e.route < B200_ROUTE_TOP_SOFTMAX || e.route > B200_ROUTE_SIGMOID_TOP)
                 return bad(at + "unknown expert activation or routing rule");
+            if (e.act == B200_ACT_SILU_GLU && e.shared_ff > 0) return bad(at + "gated experts take no always-on expert");
+            if (e.weight_input && p.streams > 0) return bad(at + "weights on the experts' inputs are not available in the multi-stream form");
+        } else if (L.ff_kind == B200_FF_CLAMPED_GLU) {
+            if (L.ff > 0 && !(L.ff_limit > 0.0f)) return bad(at + "the clamped feed-forward needs a positive limit");
         } else if (L.ff_kind != B200_FF_RELU2 && L.ff_kind != B200_FF_GATED_GELU) return bad(at + "unknown feed-forward kind");
         if (L.ff < 0) return bad(at + "negative feed-forward width");
     }
@@ -1845,6 +1939,25 @@ int need_vec(LpModel* m, const std::string& name, uint64_t n, const float** out,
     m->weight_bytes += t->bytes;
     return B200_OK;
 }
+// The frequencies of the dims / 2 rotated pairs, f_i = base^(-2i / dims), stretched as b200_rotary_desc says when yarn_factor > 0;
+// *gain (when asked for) receives the factor on cos and sin, 1 without stretching.
+std::vector<double> rotary_frequencies(const b200_rotary_desc& ro, float* gain) {
+    const int half = ro.dims / 2;
+    std::vector<double> f(half);
+    for (int i = 0; i < half; i++) f[i] = std::pow((double)ro.base, -2.0 * (double)i / (double)ro.dims);
+    if (gain) *gain = 1.0f;
+    if (ro.yarn_factor > 0.0f) {
+        const double pi = 3.14159265358979323846;
+        auto turn_dim = [&](double t) { return (double)ro.dims * std::log((double)ro.yarn_original / (2.0 * pi * t)) / (2.0 * std::log((double)ro.base)); };
+        const double lo = std::max(std::floor(turn_dim(ro.yarn_fast)), 0.0), hi = std::min(std::ceil(turn_dim(ro.yarn_slow)), (double)ro.dims - 1.0);
+        for (int i = 0; i < half; i++) {
+            const double ramp = std::min(1.0, std::max(0.0, ((double)i - lo) / std::max(hi - lo, 0.001)));
+            f[i] = f[i] / (double)ro.yarn_factor * ramp + f[i] * (1.0 - ramp);
+        }
+        if (gain) *gain = (float)(0.1 * std::log((double)ro.yarn_factor) + 1.0);
+    }
+    return f;
+}
 int need_mat(LpModel* m, const std::string& name, uint64_t rows, uint64_t cols, void** out, std::string* err) {
     const Tensor* t = find(m, name);
     if (!t) return lp_fail(err, B200_ERR_INVALID_ARGUMENT, "missing tensor " + name);
@@ -1924,21 +2037,36 @@ int lp_finalize(LpModel* m, std::string* err) {
             m->max_act = std::max(m->max_act, L.k_cat);
             m->max_o = std::max(m->max_o, mm.heads * mm.vdim);
             m->max_q = std::max(m->max_q, a.heads * a.dim);
-        } else if (L.d.mixer == B200_MIX_SOFTMAX_ATTN) {
+        } else if (L.d.mixer == B200_MIX_SOFTMAX_ATTN || L.d.mixer == B200_MIX_ATTN_RECURRENT) {
+            // the general softmax mixer, alone ('.mix.*') or as the left branch beside a recurrent unit ('.mix.left.*', '.mix.right.*'):
+            // one input projection [q | k | v | gate | the unit's projections]
             const b200_softmax_attn_desc& a = L.d.sattn;
-            const std::string x = pre + "mix.";
+            const bool dual = L.d.mixer == B200_MIX_ATTN_RECURRENT;
+            const std::string x = pre + (dual ? "mix.left." : "mix."), rx = pre + "mix.right.";
             const uint64_t nq = (uint64_t)a.heads * a.dim, nk = (uint64_t)a.kv_heads * a.dim, nv = (uint64_t)a.kv_heads * a.vdim;
             std::vector<std::string> names = {x + "q", x + "k", x + "v"};
             std::vector<uint64_t> rows = {nq, nk, nv};
             if (a.out_gate) { names.push_back(x + "g"); rows.push_back(a.out_gate == B200_GATE_HEAD ? (uint64_t)a.heads : (uint64_t)a.heads * a.vdim); }
+            const size_t n_left = names.size();
+            if (dual && L.d.rec_kind == B200_REC_GATED_LINEAR) {
+                const b200_gated_linear_desc& q = L.d.glin;
+                for (const char* sfx : {"q", "v", "f"}) names.push_back(rx + sfx);
+                for (uint64_t v : {(uint64_t)q.heads * q.dim, (uint64_t)q.heads * q.vdim, (uint64_t)q.heads * q.dim}) rows.push_back(v);
+            } else if (dual) {
+                for (const char* sfx : {"z", "x", "g"}) names.push_back(rx + sfx);
+                for (int k = 0; k < 3; k++) rows.push_back((uint64_t)L.d.gunit.width);
+            }
             if ((rc = fuse_rows(m, names, rows, W, &L.w_in, &L.n_in, &off, err))) return rc;
             AttnGeom& g = L.ag;
-            g.H = a.heads; g.G = a.kv_heads; g.dim = a.dim; g.vdim = a.vdim; g.window = a.mask_size; g.keep_first = 0;
+            g.H = a.heads; g.G = a.kv_heads; g.dim = a.dim; g.vdim = a.vdim; g.keep_first = 0;
+            g.window = a.mask == B200_MASK_CAUSAL ? p.max_seq_len : a.mask_size;
             g.chunk = a.mask == B200_MASK_CHUNK ? 1 : 0; g.softcap = a.softcap; g.slope_exp = a.dist_bias_exp;
             g.qk_norm = 0; g.out_gate = a.out_gate; g.scale = a.scale; g.eps = p.norm_eps; g.cap = p.max_seq_len;
             g.q_off = off[0]; g.k_off = off[1]; g.v_off = off[2]; g.g_off = a.out_gate ? off[3] : 0;
+            g.sink_mode = a.sink;
             PrepGeom& q = L.pg;
             q.C = (int)(nq + nk + nv); q.taps = a.conv; q.qk_norm = a.qk_norm; q.rot_dims = a.rot_dims; q.v_mix = a.v_mix;
+            q.rot_after_norm = a.rot_after_norm; q.rot_gain = 1.0f; q.v_rot = a.v_rot_base > 0.0f ? 1 : 0;
             // concatenate per-part vectors ([q | k | v] order of the projection) into one device table; `per` values per channel
             auto cat3 = [&](const char* suffix, uint64_t per, const float** out) -> int {
                 const float* part[3];
@@ -1964,24 +2092,84 @@ int lp_finalize(LpModel* m, std::string* err) {
                 if ((rc = need_vec(m, x + "q.norm", whole ? nq : (uint64_t)a.dim, &L.qn, err))) return rc;
                 if ((rc = need_vec(m, x + "k.norm", whole ? nk : (uint64_t)a.dim, &L.kn, err))) return rc;
             }
-            if (a.rot_dims > 0) {   // f_i = base^(-2i / dims), in double
-                std::vector<double> f(a.rot_dims / 2);
-                for (int i = 0; i < a.rot_dims / 2; i++) f[i] = std::pow((double)a.rot_base, -2.0 * (double)i / (double)a.rot_dims);
+            // a table of doubles on the device, owned by the tensor map under `name`
+            auto freq_table = [&](const std::vector<double>& f, const std::string& name, const double** out) -> int {
                 double* d = nullptr;
                 LCU_ALLOC(cudaMalloc((void**)&d, up16(f.size() * 8)));
                 LCU(cudaMemcpy(d, f.data(), f.size() * 8, cudaMemcpyHostToDevice));
                 Tensor t;
                 t.d = d; t.rows = 1; t.cols = f.size(); t.bytes = f.size() * 8;
-                m->tensors[x + "rot.freq"] = t;
-                L.rot_freq = d;
+                m->tensors[name] = t;
+                *out = d;
+                return B200_OK;
+            };
+            if (a.rot_dims > 0) {   // the pairs' frequencies in double, stretched when yarn_factor > 0 (b200_rotary_desc)
+                const b200_rotary_desc ro{a.rot_dims, a.rot_base, a.yarn_factor, a.yarn_original, a.yarn_fast, a.yarn_slow};
+                if ((rc = freq_table(rotary_frequencies(ro, &q.rot_gain), x + "rot.freq", &L.rot_freq))) return rc;
             }
+            if (q.v_rot) {          // the values' own frequencies: v_rot_base^(-2m / vdim), never stretched
+                const b200_rotary_desc ro{a.vdim, a.v_rot_base, 0.0f, 0.0f, 0.0f, 0.0f};
+                if ((rc = freq_table(rotary_frequencies(ro, nullptr), x + "vrot.freq", &L.v_freq))) return rc;
+                m->max_vrot = std::max(m->max_vrot, a.vdim);
+            }
+            if (a.sink == B200_SINK_LEARNED && (rc = need_vec(m, x + "sink", a.heads, &L.sink, err))) return rc;
+            if (a.o_bias && (rc = need_vec(m, x + "o.b", W, &L.o_bias, err))) return rc;
             if (a.v_mix == B200_VMIX_BLEND && (rc = need_vec(m, x + "vmix", 1, &L.vmix, err))) return rc;
-            if ((rc = need_mat(m, x + "o", W, (uint64_t)a.heads * a.vdim, &L.wo, err))) return rc;
+            L.k_left = a.heads * a.vdim;
             L.kv_bytes = up16((size_t)p.max_seq_len * (nk + nv) * 4);
-            L.rec_bytes = q.taps > 1 ? up16((size_t)(q.taps - 1) * q.C * 4) : 0;
-            m->max_act = std::max(m->max_act, a.heads * a.vdim);
+            const size_t tail_bytes = q.taps > 1 ? up16((size_t)(q.taps - 1) * q.C * 4) : 0;
+            L.rec_bytes = tail_bytes;
             m->max_q = std::max(m->max_q, (int)nq);
             if (a.v_mix != B200_VMIX_NONE) m->max_vsrc = std::max(m->max_vsrc, (int)nv);
+            if (!dual) {
+                if ((rc = need_mat(m, x + "o", W, (uint64_t)L.k_left, &L.wo, err))) return rc;
+                m->max_act = std::max(m->max_act, L.k_left);
+            } else {
+                // the unit's state sits behind the convolution tail in the run's state block
+                if (L.d.rec_kind == B200_REC_GATED_LINEAR) {
+                    const b200_gated_linear_desc& u = L.d.glin;
+                    GlinGeom& gg = L.gl;
+                    gg.H = u.heads; gg.dim = u.dim; gg.vdim = u.vdim; gg.q_off = off[n_left]; gg.v_off = off[n_left + 1]; gg.f_off = off[n_left + 2];
+                    gg.rec_off = tail_bytes;
+                    if ((rc = need_vec(m, rx + "f.b", (uint64_t)u.heads * u.dim, &L.rec_b0, err))) return rc;
+                    if ((rc = need_vec(m, rx + "lower", (uint64_t)u.heads * u.dim, &L.rec_lower, err))) return rc;
+                    if ((rc = need_vec(m, rx + "norm", u.vdim, &L.rec_norm, err))) return rc;
+                    L.k_right = u.heads * u.vdim;
+                    L.rec_bytes += up16((size_t)u.heads * u.dim * u.vdim * 4);
+                    m->max_o = std::max(m->max_o, L.k_right);
+                } else {
+                    GunitGeom& gg = L.gu;
+                    gg.width = L.d.gunit.width; gg.z_off = off[n_left]; gg.x_off = off[n_left + 1]; gg.g_off = off[n_left + 2];
+                    gg.rec_off = tail_bytes;
+                    if ((rc = need_vec(m, rx + "z.b", gg.width, &L.rec_b0, err))) return rc;
+                    if ((rc = need_vec(m, rx + "x.b", gg.width, &L.rec_b1, err))) return rc;
+                    L.k_right = gg.width;
+                    L.rec_bytes += up16((size_t)gg.width * 4);
+                }
+                L.k_cat = L.k_left + L.k_right;
+                m->max_act = std::max(m->max_act, L.k_cat);
+                if (L.d.combine == B200_COMBINE_WEIGHTED) {
+                    // the two output projections side by side: one product [left | right] x [W_o left | W_o right]^T
+                    if (a.o_bias) return lp_fail(err, B200_ERR_UNSUPPORTED, pre + "mix: an output bias with weighted branches is not supported");
+                    void *wa, *wm;
+                    const size_t Ka = (size_t)L.k_left, Kb = (size_t)L.k_right, es = elt(m);
+                    if ((rc = need_mat(m, x + "o", W, Ka, &wa, err))) return rc;
+                    if ((rc = need_mat(m, rx + "o", W, Kb, &wm, err))) return rc;
+                    LCU_ALLOC(cudaMalloc(&L.wo_cat, up16(W * (Ka + Kb) * es)));
+                    LCU(cudaMemcpy2D(L.wo_cat, (Ka + Kb) * es, wa, Ka * es, Ka * es, W, cudaMemcpyDeviceToDevice));
+                    LCU(cudaMemcpy2D((uint8_t*)L.wo_cat + Ka * es, (Ka + Kb) * es, wm, Kb * es, Kb * es, W, cudaMemcpyDeviceToDevice));
+                    for (const std::string& nm : {x + "o", rx + "o"}) {
+                        cudaFree(m->tensors[nm].d);
+                        m->tensors.erase(nm);
+                    }
+                } else {
+                    if ((rc = need_mat(m, x + "o", W, (uint64_t)L.k_left, &L.wo, err))) return rc;
+                    if ((rc = need_mat(m, rx + "o", W, (uint64_t)L.k_right, &L.wo_right, err))) return rc;
+                    if ((rc = need_vec(m, pre + "mix.left.out", W, &L.left_out, err))) return rc;
+                    if ((rc = need_vec(m, pre + "mix.right.out", W, &L.right_out, err))) return rc;
+                    m->need_y2 = true;
+                }
+            }
         } else if (L.d.mixer == B200_MIX_LATENT_ATTN) {
             const b200_latent_attn_desc& a = L.d.latent;
             const std::string x = pre + "mix.";
@@ -2017,21 +2205,7 @@ int lp_finalize(LpModel* m, std::string* err) {
                 L.w_ukT = t.d;
             }
             if (a.rot.dims > 0) {   // frequencies of the pairs, in double (see b200_rotary_desc)
-                const b200_rotary_desc& ro = a.rot;
-                const int half = ro.dims / 2;
-                std::vector<double> f(half);
-                for (int i = 0; i < half; i++) f[i] = std::pow((double)ro.base, -2.0 * (double)i / (double)ro.dims);
-                g.rot_mult = 1.0f;
-                if (ro.yarn_factor > 0.0f) {
-                    const double pi = 3.14159265358979323846;
-                    auto turn_dim = [&](double t) { return (double)ro.dims * std::log((double)ro.yarn_original / (2.0 * pi * t)) / (2.0 * std::log((double)ro.base)); };
-                    const double lo = std::max(std::floor(turn_dim(ro.yarn_fast)), 0.0), hi = std::min(std::ceil(turn_dim(ro.yarn_slow)), (double)ro.dims - 1.0);
-                    for (int i = 0; i < half; i++) {
-                        const double ramp = std::min(1.0, std::max(0.0, ((double)i - lo) / std::max(hi - lo, 0.001)));
-                        f[i] = f[i] / (double)ro.yarn_factor * ramp + f[i] * (1.0 - ramp);
-                    }
-                    g.rot_mult = (float)(0.1 * std::log((double)ro.yarn_factor) + 1.0);
-                }
+                const std::vector<double> f = rotary_frequencies(a.rot, &g.rot_mult);
                 double* d = nullptr;
                 LCU_ALLOC(cudaMalloc((void**)&d, up16(f.size() * 8)));
                 LCU(cudaMemcpy(d, f.data(), f.size() * 8, cudaMemcpyHostToDevice));
@@ -2114,12 +2288,39 @@ int lp_finalize(LpModel* m, std::string* err) {
                 if ((rc = need_vec(m, hc + "mix", (uint64_t)p.streams * p.streams, &L.hc_mix[q], err))) return rc;
             }
         }
+        // parallel_ff: the feed-forward reads the mixer's normed input, so its first projection ([gate | up], [up] or the router) joins
+        // the layer's input projection: one product per layer for everything that reads the norm; there is no second norm
+        const bool par = p.parallel_ff != 0;
+        auto join_input = [&](const std::vector<std::string>& names, const std::vector<uint64_t>& rows) -> int {
+            void* cat = nullptr;
+            int n_cat = 0;
+            std::vector<int> o2;
+            if ((rc = fuse_rows(m, names, rows, W, &cat, &n_cat, &o2, err))) return rc;
+            void* both = nullptr;
+            const size_t es = elt(m), a = (size_t)L.n_in * W * es, b = (size_t)n_cat * W * es;
+            LCU_ALLOC(cudaMalloc(&both, up16(a + b)));
+            LCU(cudaMemcpy(both, L.w_in, a, cudaMemcpyDeviceToDevice));
+            LCU(cudaMemcpy((uint8_t*)both + a, cat, b, cudaMemcpyDeviceToDevice));
+            cudaFree(L.w_in);
+            cudaFree(cat);
+            L.w_in = both;
+            L.ff_off = L.n_in;
+            L.n_in += n_cat;
+            m->max_in = std::max(m->max_in, L.n_in);
+            return B200_OK;
+        };
         if (L.d.ff_kind == B200_FF_MOE) {
             const b200_moe_desc& e = L.d.moe;
-            if ((rc = need_vec(m, pre + "norm2", W, &L.norm2, err))) return rc;
-            std::vector<std::string> names = {pre + "mlp.router"}, down;
-            std::vector<uint64_t> rows = {(uint64_t)e.experts};
+            if (!par && (rc = need_vec(m, pre + "norm2", W, &L.norm2, err))) return rc;
+            const bool glu = e.act == B200_ACT_SILU_GLU;
+            const int per = glu ? 2 * e.expert_ff : e.expert_ff;   // rows of one expert's up matrix ([gate | up] when gated)
+            if (par && (rc = join_input({pre + "mlp.router"}, {(uint64_t)e.experts}))) return rc;
+            std::vector<std::string> names, down;
+            std::vector<uint64_t> rows;
+            if (!par) { names.push_back(pre + "mlp.router"); rows.push_back((uint64_t)e.experts); }
+            L.up_router_rows = par ? 0 : e.experts;
             for (int i = 0; i < e.experts; i++) {
+                if (glu) { names.push_back(pre + "mlp.e" + std::to_string(i) + ".gate"); rows.push_back(e.expert_ff); }
                 names.push_back(pre + "mlp.e" + std::to_string(i) + ".up");
                 rows.push_back(e.expert_ff);
                 down.push_back(pre + "mlp.e" + std::to_string(i) + ".down");
@@ -2152,13 +2353,19 @@ int lp_finalize(LpModel* m, std::string* err) {
             t.d = L.w_down; t.matrix = true; t.rows = W; t.cols = L.k_down; t.bytes = W * (size_t)L.k_down * es;
             m->tensors[pre + "mlp.down_cat"] = t;
             m->max_act = std::max(m->max_act, L.k_down);
-            m->max_in = std::max(m->max_in, L.n_up);
-            m->weight_bytes -= (size_t)(e.experts - e.top) * 2 * e.expert_ff * W * es;   // a token reads its chosen experts only
+            m->max_in = std::max(m->max_in, std::max(L.n_up, e.experts * per));
+            m->weight_bytes -= (size_t)(e.experts - e.top) * (per + e.expert_ff) * W * es;   // a token reads its chosen experts only
             m->max_experts = std::max(m->max_experts, e.experts);
             m->max_top = std::max(m->max_top, e.top);
         } else if (L.d.ff > 0) {
-            if ((rc = need_vec(m, pre + "norm2", W, &L.norm2, err))) return rc;
-            if (L.d.ff_kind == B200_FF_GATED_GELU) {
+            if (!par && (rc = need_vec(m, pre + "norm2", W, &L.norm2, err))) return rc;
+            const bool two = L.d.ff_kind == B200_FF_GATED_GELU || L.d.ff_kind == B200_FF_CLAMPED_GLU;
+            if (par) {
+                if (two) rc = join_input({pre + "mlp.gate", pre + "mlp.up"}, {(uint64_t)L.d.ff, (uint64_t)L.d.ff});
+                else rc = join_input({pre + "mlp.up"}, {(uint64_t)L.d.ff});
+                if (rc) return rc;
+                L.n_up = two ? 2 * L.d.ff : L.d.ff;
+            } else if (two) {
                 std::vector<int> uoff;
                 if ((rc = fuse_rows(m, {pre + "mlp.gate", pre + "mlp.up"}, {(uint64_t)L.d.ff, (uint64_t)L.d.ff}, W, &L.w_up, &L.n_up, &uoff, err))) return rc;
                 Tensor t;
@@ -2179,7 +2386,8 @@ int lp_finalize(LpModel* m, std::string* err) {
     {   // the preparation kernel of the softmax mixer keeps a row's q, k, v in shared memory
         size_t need = 0;
         for (const LayerPlan& L : m->plan)
-            if (L.d.mixer == B200_MIX_SOFTMAX_ATTN) need = std::max(need, (size_t)(((L.pg.C + 3) & ~3) + L.pg.rot_dims) * 4);
+            if (L.d.mixer == B200_MIX_SOFTMAX_ATTN || L.d.mixer == B200_MIX_ATTN_RECURRENT)
+                need = std::max(need, (size_t)(((L.pg.C + 3) & ~3) + L.pg.rot_dims + (L.pg.v_rot ? L.ag.vdim : 0)) * 4);
         if (need > 200 * 1024) return lp_fail(err, B200_ERR_UNSUPPORTED, "softmax mixer: q, k and v of one token exceed 200 KB of shared memory");
         if (need > 48 * 1024) LCU(cudaFuncSetAttribute(lp_attn_prep2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)need));
     }
@@ -2203,7 +2411,8 @@ int lp_finalize(LpModel* m, std::string* err) {
         rec += L.rec_bytes;
         m->weight_bytes += 0;
         if (L.d.mixer == B200_MIX_WINDOW_MEMORY) m->kv_bytes_per_pos += (size_t)L.d.attn.kv_heads * (L.d.attn.dim + L.d.attn.vdim) * 4;
-        if (L.d.mixer == B200_MIX_SOFTMAX_ATTN) m->kv_bytes_per_pos += (size_t)L.d.sattn.kv_heads * (L.d.sattn.dim + L.d.sattn.vdim) * 4;
+        if (L.d.mixer == B200_MIX_SOFTMAX_ATTN || L.d.mixer == B200_MIX_ATTN_RECURRENT)
+            m->kv_bytes_per_pos += (size_t)L.d.sattn.kv_heads * (L.d.sattn.dim + L.d.sattn.vdim) * 4;
         if (L.d.mixer == B200_MIX_LATENT_ATTN && L.d.latent.kv_from < 0) m->kv_bytes_per_pos += (size_t)(L.d.latent.kv_rank + L.d.latent.rot_dim) * 4;
     }
     m->slot_kv_bytes = std::max<size_t>(kv, 256);
@@ -2254,7 +2463,7 @@ void lp_destroy(LpModel* m) {
     for (SlotMem& s : m->pool) { cudaFree(s.kv); cudaFree(s.rec); }
     for (void* ptr : {(void*)m->inv_freq, (void*)m->d_meta, (void*)m->x, (void*)m->P, (void*)m->qbuf, (void*)m->O, (void*)m->conv, (void*)m->logits,
                       m->hn, m->act_a, m->hw, (void*)m->pick, (void*)m->taps, (void*)m->y, (void*)m->vsrc, (void*)m->moe_w, (void*)m->moe_selw,
-                      (void*)m->moe_sel, (void*)m->moe_pos, (void*)m->moe_seg, m->moe_xp, (void*)m->moe_yp, (void*)m->xs, m->cq})
+                      (void*)m->moe_sel, (void*)m->moe_pos, (void*)m->moe_seg, m->moe_xp, (void*)m->moe_yp, (void*)m->xs, m->cq, (void*)m->vrot})
         cudaFree(ptr);
     if (m->h_meta) cudaFreeHost(m->h_meta);
     if (m->h_logits) cudaFreeHost(m->h_logits);
@@ -2320,7 +2529,8 @@ int ensure_scratch(LpModel* m, int R, int n_runs, int n_want, std::string* err) 
         if ((rc = grow(&m->conv, (size_t)cap * std::max(m->max_conv, 1) * 4, err))) return rc;
         if ((rc = grow(&m->hn, (size_t)cap * W * es, err))) return rc;
         if ((rc = grow(&m->act_a, (size_t)cap * m->max_act * es, err))) return rc;
-        if ((m->p.post_norm || m->max_experts > 0 || m->p.streams > 0) && (rc = grow(&m->y, (size_t)cap * W * 4, err))) return rc;
+        if ((m->p.post_norm || m->max_experts > 0 || m->p.streams > 0 || m->need_y2) && (rc = grow(&m->y, (size_t)cap * W * (m->need_y2 ? 8 : 4), err))) return rc;
+        if (m->max_vrot > 0 && (rc = grow(&m->vrot, (size_t)cap * m->max_vrot * 4, err))) return rc;
         if (m->p.streams > 0 && (rc = grow(&m->xs, (size_t)cap * m->p.streams * W * 4, err))) return rc;
         if (m->max_qrank > 0 && (rc = grow(&m->cq, (size_t)cap * m->max_qrank * es, err))) return rc;
         if (m->max_vsrc > 0 && (rc = grow(&m->vsrc, (size_t)cap * m->max_vsrc * 4, err))) return rc;
@@ -2384,7 +2594,7 @@ bool attn_tile(LpModel* m, const StepMeta& sm, const AttnGeom& ag, int ldp, int 
 // The warp kernel: any row count, both compute modes.
 void attn_rows(LpModel* m, const StepMeta& sm, const AttnGeom& ag, const LayerPlan& L, int R) {
     dim3 agrid(R, ag.H);
-    const size_t asmem = (size_t)(((ag.dim + 3) & ~3) + ATT_WARPS * ag.vdim + 2 * ATT_WARPS) * 4;
+    const size_t asmem = (size_t)(((ag.dim + 3) & ~3) + ATT_WARPS * ag.vdim + 2 * ATT_WARPS + (ag.vrot ? ag.vdim : 0)) * 4;
     const int vch = ag.vdim <= 128 ? 4 : ag.vdim <= 256 ? 8 : 16;
 #define LP_ATTN(T, V) launch(m, lp_window_attn_kernel<T, V>, agrid, dim3(32 * ATT_WARPS), asmem, sm, ag, (const float*)m->qbuf, (const float*)m->P, L.n_in, L.qn, L.kn, (T*)m->act_a)
     if (m->f32) {
@@ -2473,7 +2683,7 @@ void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want,
             boundary(cur->hc_in[sub], nw, nullptr);
             gemm(m, m->hn, W, Wm, N, W, Y, ldy, R, 1.0f, epi);
         } else if (post) gemm(m, m->hn, W, Wm, N, W, Y, ldy, R, 1.0f, epi);
-        else norm_gemm(m, m->x, add, nullptr, nw, m->hn, Wm, N, Y, ldy, R, 1.0f, epi);
+        else norm_gemm(m, m->x, add, nullptr, nw, m->hn, Wm, N, Y, ldy, R, 1.0f, epi, p.parallel_ff != 0);   // (parallel_ff: the experts read m->hn later)
     };
     // Few rows (decoding) in the norm-after-sum form: the kernel that writes m->y also does what follows it -- its last block norms the
     // rows and, when `moe` follows, computes the router's logits and choices (rows_tail) -- instead of two or three more launches.
@@ -2488,21 +2698,21 @@ void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want,
         }
         return t;
     };
-    auto project_out = [&](const void* X, int K, const void* Wm, const float* nw, const LayerPlan* moe) {
+    auto project_out = [&](const void* X, int K, const void* Wm, const float* nw, const LayerPlan* moe, const float* bias = nullptr) {
         if (sfew) {
             const RowsTail t = stream_tail();
-            gemm(m, X, K, Wm, W, K, m->y, W, R, 1.0f, EPI_STORE, &t);
+            gemm(m, X, K, Wm, W, K, m->y, W, R, 1.0f, EPI_STORE, &t, bias);
             pre_done = true;
         } else if (streams) {
-            gemm(m, X, K, Wm, W, K, m->y, W, R, 1.0f, EPI_STORE);
+            gemm(m, X, K, Wm, W, K, m->y, W, R, 1.0f, EPI_STORE, nullptr, bias);
             pend.y = m->y; pend.mix = cur->hc_mix[sub]; pend.out = cur->hc_out[sub];
         } else if (few) {
             const RowsTail t = make_tail(nw, moe);
-            gemm(m, X, K, Wm, W, K, m->y, W, R, 1.0f, EPI_STORE, &t);
+            gemm(m, X, K, Wm, W, K, m->y, W, R, 1.0f, EPI_STORE, &t, bias);
         } else if (post) {
-            gemm(m, X, K, Wm, W, K, m->y, W, R, 1.0f, EPI_STORE);
+            gemm(m, X, K, Wm, W, K, m->y, W, R, 1.0f, EPI_STORE, nullptr, bias);
             cast_x(m->y, nw);
-        } else gemm(m, X, K, Wm, W, K, m->x, W, R, 1.0f, EPI_ADD);
+        } else gemm(m, X, K, Wm, W, K, m->x, W, R, 1.0f, EPI_ADD, nullptr, bias);
     };
     if (post) cast_x(nullptr, nullptr);
     for (size_t run = 0; run < m->runs.size(); run++) {
@@ -2517,21 +2727,65 @@ void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want,
         cur_run = run;
         cur_moe_sel = moe_sel_ok;
         project_in(add, L.norm1, L.w_in, L.n_in, m->P, L.n_in, EPI_STORE);
-        if (L.d.mixer == B200_MIX_SOFTMAX_ATTN) {
+        if (L.d.mixer == B200_MIX_SOFTMAX_ATTN || L.d.mixer == B200_MIX_ATTN_RECURRENT) {
+            const bool dual = L.d.mixer == B200_MIX_ATTN_RECURRENT, weighted = dual && L.d.combine == B200_COMBINE_WEIGHTED;
             AttnGeom ag = L.ag;
             ag.kv_off = m->run_kv_off[run];
-            ag.out_ld = ag.H * ag.vdim;
-            ag.out_scale = 1.0f;
+            ag.out_ld = dual ? L.k_cat : L.k_left;          // the two branches' operands side by side: [left | right]
+            ag.out_scale = weighted ? L.d.attn_scale : 1.0f;
             ag.fused_prep = 0;
+            ag.sink = L.sink;
+            ag.vrot = L.pg.v_rot ? m->vrot : nullptr;
             PrepGeom pg = L.pg;
             pg.rec_off = m->run_rec_off[run];
-            const size_t psmem = (size_t)(((pg.C + 3) & ~3) + pg.rot_dims) * 4;
+            const size_t psmem = (size_t)(((pg.C + 3) & ~3) + pg.rot_dims + (pg.v_rot ? ag.vdim : 0)) * 4;
             const int shift = (m->use_fuse && max_len == 1) ? 1 : 0;   // one row per run: the row's block moves the run's tail on itself
             launch(m, lp_attn_prep2_kernel, dim3(R), dim3(256), psmem, sm, ag, pg, (const float*)m->P, L.n_in, L.qkv_bias, L.conv_w, L.qn, L.kn, L.rot_freq,
-                   L.vmix, m->vsrc, m->qbuf, shift);
+                   L.vmix, m->vsrc, m->qbuf, shift, L.v_freq, m->vrot);
             if (pg.taps > 1 && !shift) launch(m, lp_attn_conv_tail_kernel, dim3(n_runs), dim3(256), 0, sm, pg, (const float*)m->P, L.n_in, L.qkv_bias);
             if (!attn_tile(m, sm, ag, L.n_in, n_runs, max_len)) attn_rows(m, sm, ag, L, R);
-            project_out(m->act_a, ag.out_ld, L.wo, L.norm1, moe_next);
+            if (!dual) {
+                project_out(m->act_a, ag.out_ld, L.wo, L.norm1, moe_next, L.o_bias);
+            } else {
+                const size_t es = elt(m);
+                void* right = (uint8_t*)m->act_a + (size_t)L.k_left * es;      // the unit's output, column k_left on
+                const float rscale = weighted ? L.d.mem_scale : 1.0f;
+                if (L.d.rec_kind == B200_REC_GATED_LINEAR) {
+                    GlinGeom gg = L.gl;
+                    gg.rec_off += m->run_rec_off[run];
+                    const int ldo = gg.H * gg.vdim;
+                    const int cols = SCAN_BD / (pick_dmax(gg.dim) / SCAN_DREG);
+                    dim3 sgrid((gg.vdim + cols - 1) / cols, gg.H, n_runs);
+#define LP_GLIN(DM) launch(m, lp_gated_linear_kernel<DM>, sgrid, dim3(SCAN_BD), 0, sm, gg, (const float*)m->P, L.n_in, L.rec_b0, L.rec_lower, m->O, ldo)
+                    switch (pick_dmax(gg.dim)) {
+                        case 32: LP_GLIN(32); break;
+                        case 64: LP_GLIN(64); break;
+                        case 128: LP_GLIN(128); break;
+                        default: LP_GLIN(256); break;
+                    }
+#undef LP_GLIN
+                    dim3 hgrid(R, (gg.H + 3) / 4);   // per-head unit RMS times the shared weight, no gate
+                    if (m->f32) launch(m, lp_headnorm_gate_kernel<float>, hgrid, dim3(128), 0, (const float*)m->O, ldo, (const float*)m->P, L.n_in, 0, L.rec_norm, 1, gg.H, gg.vdim, p.norm_eps, 2, (float*)right, L.k_cat, rscale, R);
+                    else launch(m, lp_headnorm_gate_kernel<bf16>, hgrid, dim3(128), 0, (const float*)m->O, ldo, (const float*)m->P, L.n_in, 0, L.rec_norm, 1, gg.H, gg.vdim, p.norm_eps, 2, (bf16*)right, L.k_cat, rscale, R);
+                } else {
+                    GunitGeom gg = L.gu;
+                    gg.rec_off += m->run_rec_off[run];
+                    dim3 ugrid((gg.width + GU_CH - 1) / GU_CH, n_runs), ublock(GU_CH, GU_SEG);
+                    if (m->f32) launch(m, lp_gated_unit_kernel<float>, ugrid, ublock, 0, sm, gg, (const float*)m->P, L.n_in, L.rec_b0, L.rec_b1, (float*)right, L.k_cat, rscale);
+                    else launch(m, lp_gated_unit_kernel<bf16>, ugrid, ublock, 0, sm, gg, (const float*)m->P, L.n_in, L.rec_b0, L.rec_b1, (bf16*)right, L.k_cat, rscale);
+                }
+                if (weighted) {
+                    project_out(m->act_a, L.k_cat, L.wo_cat, L.norm1, moe_next);
+                } else {
+                    // each branch through its own output projection, rms norm with its plain weight, half the sum: the sublayer's output
+                    float* ya = m->y;
+                    float* yb = m->y + (size_t)R * W;
+                    // (norm-first form only: the sum goes straight into the residual stream)
+                    gemm_ld(m, m->act_a, L.k_cat, L.wo, L.k_left, W, L.k_left, ya, W, R, EPI_STORE, L.o_bias);
+                    gemm_ld(m, right, L.k_cat, L.wo_right, L.k_right, W, L.k_right, yb, W, R, EPI_STORE);
+                    launch(m, lp_dual_norm_add_kernel, dim3(R), dim3(256), 0, m->x, (const float*)ya, (const float*)yb, W, L.left_out, L.right_out, W, p.norm_eps, 0.5f);
+                }
+            }
         } else if (L.d.mixer == B200_MIX_WINDOW_MEMORY) {
             AttnGeom ag = L.ag;
             ag.kv_off = m->run_kv_off[run];
@@ -2623,21 +2877,28 @@ void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want,
             else launch(m, lp_headnorm_gate_kernel<bf16>, hgrid, dim3(128), 0, (const float*)m->O, ldo, (const float*)m->P, L.n_in, dg.g_off, L.delta_norm, 1, dg.H, dg.vdim, p.norm_eps, 1, (bf16*)m->act_a, ldo, 1.0f, R);
             project_out(m->act_a, ldo, L.wo_delta, L.norm1, moe_next);
         }
+        const bool par = p.parallel_ff != 0;
         if (L.d.ff_kind == B200_FF_MOE) {
-            // The operand is m->hn in both layer forms; the router's rows come first in w_up ([router | e0 up | ... | always-on up]).
+            // The operand is m->hn in every layer form; the router's rows come first in w_up ([router | e0 up | ... | always-on up]) or,
+            // with parallel_ff, sit in the layer's input projection (their logits are columns ff_off .. of m->P already).
             // Router logits (f32) -> the choice per row -> the experts -> m->y -> the residual.
             const b200_moe_desc& e = L.d.moe;
             const size_t es = elt(m);
             const int act_epi = e.act == B200_ACT_GELU ? EPI_GELU : EPI_RELU2;
+            const int per = e.act == B200_ACT_SILU_GLU ? 2 * e.expert_ff : e.expert_ff;      // rows of one expert's up matrix
+            const bool own_act = e.act == B200_ACT_SILU_GLU || e.weight_input != 0;            // the hidden units need a kernel of their own
             sub = 1;
             if (streams) boundary(L.hc_in[1], L.norm2, nullptr);
-            else if (!post) rmsnorm(m, m->x, nullptr, L.norm2, m->hn, nullptr, R);
-            if (!moe_next) {
+            else if (!post && !par) rmsnorm(m, m->x, nullptr, L.norm2, m->hn, nullptr, R);
+            if (par) {
+                launch(m, lp_moe_route_kernel, dim3((R + 3) / 4), dim3(128), 0, (const float*)m->P + L.ff_off, L.n_in, e.experts, e.top, m->moe_w, m->moe_sel, m->moe_selw, R, e.route, e.route_scale);
+            } else if (!moe_next) {
                 gemm(m, m->hn, W, L.w_up, e.experts, W, m->P, e.experts, R, 1.0f, EPI_STORE);
                 launch(m, lp_moe_route_kernel, dim3((R + 3) / 4), dim3(128), 0, (const float*)m->P, e.experts, e.experts, e.top, m->moe_w, m->moe_sel, m->moe_selw, R, e.route, e.route_scale);
             }
             const size_t hbytes = (size_t)R * W * es;
-            const uint8_t* up_experts = (const uint8_t*)L.w_up + (size_t)e.experts * W * es;
+            const uint8_t* up_experts = (const uint8_t*)L.w_up + (size_t)L.up_router_rows * W * es;
+            float* ydst = par ? m->x : m->y;          // parallel_ff: the experts' sum goes straight into the residual stream
             bool normed = false;
             if (moe_sel_ok) {
                 // few rows (decoding): kernels that walk each row's choices and read those experts' weights only
@@ -2647,11 +2908,11 @@ void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want,
                 normed = few || sfew;
                 if (sfew) pre_done = true;
                 if (m->f32) {
-                    launch(m, lp_moe_up_sel_kernel<float>, ugrid, dim3(256), hbytes, (const float*)m->hn, (const float*)L.w_up, (const int*)m->moe_sel, (const float*)m->moe_selw, e.experts, e.top, e.expert_ff, e.shared_ff, W, R, (float*)m->act_a, e.act);
-                    launch(m, lp_moe_down_sel_kernel<float>, dgrid, dim3(256), 0, (const float*)m->act_a, (const float*)L.w_down, (const int*)m->moe_sel, e.experts, e.top, e.expert_ff, e.shared_ff, W, R, m->y, t);
+                    launch(m, lp_moe_up_sel_kernel<float>, ugrid, dim3(256), hbytes, (const float*)m->hn, (const float*)up_experts, (const int*)m->moe_sel, (const float*)m->moe_selw, e.experts, e.top, e.expert_ff, e.shared_ff, W, R, (float*)m->act_a, e.act, e.weight_input);
+                    launch(m, lp_moe_down_sel_kernel<float>, dgrid, dim3(256), 0, (const float*)m->act_a, (const float*)L.w_down, (const int*)m->moe_sel, e.experts, e.top, e.expert_ff, e.shared_ff, W, R, ydst, t, par ? 1 : 0);
                 } else {
-                    launch(m, lp_moe_up_sel_kernel<bf16>, ugrid, dim3(256), hbytes, (const bf16*)m->hn, (const bf16*)L.w_up, (const int*)m->moe_sel, (const float*)m->moe_selw, e.experts, e.top, e.expert_ff, e.shared_ff, W, R, (bf16*)m->act_a, e.act);
-                    launch(m, lp_moe_down_sel_kernel<bf16>, dgrid, dim3(256), 0, (const bf16*)m->act_a, (const bf16*)L.w_down, (const int*)m->moe_sel, e.experts, e.top, e.expert_ff, e.shared_ff, W, R, m->y, t);
+                    launch(m, lp_moe_up_sel_kernel<bf16>, ugrid, dim3(256), hbytes, (const bf16*)m->hn, (const bf16*)up_experts, (const int*)m->moe_sel, (const float*)m->moe_selw, e.experts, e.top, e.expert_ff, e.shared_ff, W, R, (bf16*)m->act_a, e.act, e.weight_input);
+                    launch(m, lp_moe_down_sel_kernel<bf16>, dgrid, dim3(256), 0, (const bf16*)m->act_a, (const bf16*)L.w_down, (const int*)m->moe_sel, e.experts, e.top, e.expert_ff, e.shared_ff, W, R, ydst, t, par ? 1 : 0);
                 }
             } else if (m->use_fuse && R > 2 * GV_ROWS) {
                 // many rows: the (token, choice) pairs in expert order, one product pair per expert over its block of rows (the row
@@ -2662,34 +2923,59 @@ void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want,
                 else launch(m, lp_moe_gather_kernel<bf16>, dim3(pairs), dim3(128), 0, (const bf16*)m->hn, (const int*)m->moe_pos, e.top, W, (bf16*)m->moe_xp);
                 const uint8_t* down = (const uint8_t*)L.w_down;
                 uint8_t* act_sh = (uint8_t*)m->act_a + (size_t)pairs * e.expert_ff * es;     // the always-on expert's activations behind the others
-                gemm_grouped(m, m->moe_xp, W, up_experts, W, (size_t)e.expert_ff * W, e.experts, e.expert_ff, W, m->act_a, e.expert_ff, R, act_epi, m->moe_seg);
+                if (own_act) {
+                    // pre-activations in f32 (m->P: its router columns have been read), then the units with the pair's weight
+                    gemm_grouped(m, m->moe_xp, W, up_experts, W, (size_t)per * W, e.experts, per, W, m->P, per, R, EPI_STORE, m->moe_seg);
+                    const unsigned nb = (unsigned)(((size_t)pairs * e.expert_ff + 255) / 256);
+                    if (m->f32) launch(m, lp_moe_pair_act_kernel<float>, dim3(nb), dim3(256), 0, (const float*)m->P, per, (const int*)m->moe_pos, (const float*)m->moe_selw, e.expert_ff, (float*)m->act_a, pairs, e.act, e.weight_input);
+                    else launch(m, lp_moe_pair_act_kernel<bf16>, dim3(nb), dim3(256), 0, (const float*)m->P, per, (const int*)m->moe_pos, (const float*)m->moe_selw, e.expert_ff, (bf16*)m->act_a, pairs, e.act, e.weight_input);
+                } else {
+                    gemm_grouped(m, m->moe_xp, W, up_experts, W, (size_t)e.expert_ff * W, e.experts, e.expert_ff, W, m->act_a, e.expert_ff, R, act_epi, m->moe_seg);
+                }
                 gemm_grouped(m, m->act_a, e.expert_ff, down, L.k_down, (size_t)e.expert_ff, e.experts, W, e.expert_ff, m->moe_yp, W, R, EPI_STORE, m->moe_seg);
                 if (e.shared_ff > 0) {
-                    gemm(m, m->hn, W, up_experts + (size_t)e.experts * e.expert_ff * W * es, e.shared_ff, W, act_sh, e.shared_ff, R, 1.0f, act_epi);
-                    gemm_ld(m, act_sh, e.shared_ff, down + (size_t)e.experts * e.expert_ff * es, L.k_down, W, e.shared_ff, m->y, W, R, EPI_STORE);
+                    gemm(m, m->hn, W, up_experts + (size_t)e.experts * per * W * es, e.shared_ff, W, act_sh, e.shared_ff, R, 1.0f, act_epi);
+                    gemm_ld(m, act_sh, e.shared_ff, down + (size_t)e.experts * e.expert_ff * es, L.k_down, W, e.shared_ff, ydst, W, R, par ? EPI_ADD : EPI_STORE);
                 }
-                launch(m, lp_moe_combine_kernel, dim3(R), dim3(256), 0, (const float*)m->moe_yp, (const int*)m->moe_pos, (const float*)m->moe_selw, e.top, W, e.shared_ff > 0 ? 1 : 0, m->y);
+                launch(m, lp_moe_combine_kernel, dim3(R), dim3(256), 0, (const float*)m->moe_yp, (const int*)m->moe_pos, own_act ? (const float*)nullptr : (const float*)m->moe_selw, e.top, W,
+                       (par || e.shared_ff > 0) ? 1 : 0, ydst);
             } else {
                 // the plain form: every expert's up projection for every row, activations times their expert's weight (0 for experts
                 // that were not chosen), one product with the down matrices side by side
-                const int n_exp = L.n_up - e.experts;
+                const int n_exp = L.n_up - L.up_router_rows;
                 gemm(m, m->hn, W, up_experts, n_exp, W, m->P, n_exp, R, 1.0f, EPI_STORE);
                 const unsigned nb = (unsigned)(((size_t)R * L.k_down + 255) / 256);
-                if (m->f32) launch(m, lp_moe_act_kernel<float>, dim3(nb), dim3(256), 0, (const float*)m->P, n_exp, 0, (const float*)m->moe_w, e.experts, e.expert_ff, L.k_down, (float*)m->act_a, R, e.act);
-                else launch(m, lp_moe_act_kernel<bf16>, dim3(nb), dim3(256), 0, (const float*)m->P, n_exp, 0, (const float*)m->moe_w, e.experts, e.expert_ff, L.k_down, (bf16*)m->act_a, R, e.act);
-                gemm(m, m->act_a, L.k_down, L.w_down, W, L.k_down, m->y, W, R, 1.0f, EPI_STORE);
+                if (m->f32) launch(m, lp_moe_act_kernel<float>, dim3(nb), dim3(256), 0, (const float*)m->P, n_exp, 0, (const float*)m->moe_w, e.experts, e.expert_ff, L.k_down, (float*)m->act_a, R, e.act, e.weight_input);
+                else launch(m, lp_moe_act_kernel<bf16>, dim3(nb), dim3(256), 0, (const float*)m->P, n_exp, 0, (const float*)m->moe_w, e.experts, e.expert_ff, L.k_down, (bf16*)m->act_a, R, e.act, e.weight_input);
+                gemm(m, m->act_a, L.k_down, L.w_down, W, L.k_down, ydst, W, R, 1.0f, par ? EPI_ADD : EPI_STORE);
             }
-            if (normed) {
+            if (normed || par) {
             } else if (streams) {
                 pend.y = m->y; pend.mix = L.hc_mix[1]; pend.out = L.hc_out[1];
             } else if (post) cast_x(m->y, L.norm2);
             else launch(m, lp_add_rows_kernel, dim3((unsigned)(((size_t)R * W + 255) / 256)), dim3(256), 0, m->x, (const float*)m->y, (size_t)R * W);
-        } else if (L.d.ff > 0 && L.d.ff_kind == B200_FF_GATED_GELU) {
+        } else if (L.d.ff > 0 && (L.d.ff_kind == B200_FF_GATED_GELU || L.d.ff_kind == B200_FF_CLAMPED_GLU)) {
+            // [gate | up] in one product (with parallel_ff: columns ff_off .. of the layer's input projection), the gated units, W_down
             sub = 1;
-            project_in(nullptr, L.norm2, L.w_up, L.n_up, m->P, L.n_up, EPI_STORE);
+            const float* ffP = m->P;
+            int ff_ld = L.n_up;
+            if (par) { ffP = m->P + L.ff_off; ff_ld = L.n_in; }
+            else project_in(nullptr, L.norm2, L.w_up, L.n_up, m->P, L.n_up, EPI_STORE);
             const unsigned nb = (unsigned)(((size_t)R * L.d.ff + 255) / 256);
-            if (m->f32) launch(m, lp_gated_gelu_kernel<float>, dim3(nb), dim3(256), 0, (const float*)m->P, L.n_up, (float*)m->act_a, L.d.ff, R);
-            else launch(m, lp_gated_gelu_kernel<bf16>, dim3(nb), dim3(256), 0, (const float*)m->P, L.n_up, (bf16*)m->act_a, L.d.ff, R);
+            if (L.d.ff_kind == B200_FF_CLAMPED_GLU) {
+                if (m->f32) launch(m, lp_clamped_glu_kernel<float>, dim3(nb), dim3(256), 0, ffP, ff_ld, (float*)m->act_a, L.d.ff, R, L.d.ff_limit, L.d.ff_slope);
+                else launch(m, lp_clamped_glu_kernel<bf16>, dim3(nb), dim3(256), 0, ffP, ff_ld, (bf16*)m->act_a, L.d.ff, R, L.d.ff_limit, L.d.ff_slope);
+            } else {
+                if (m->f32) launch(m, lp_gated_gelu_kernel<float>, dim3(nb), dim3(256), 0, ffP, ff_ld, (float*)m->act_a, L.d.ff, R);
+                else launch(m, lp_gated_gelu_kernel<bf16>, dim3(nb), dim3(256), 0, ffP, ff_ld, (bf16*)m->act_a, L.d.ff, R);
+            }
+            project_out(m->act_a, L.d.ff, L.w_down, L.norm2, nullptr);
+        } else if (L.d.ff > 0 && par) {
+            // relu^2 of the feed-forward's columns of the layer's input projection
+            sub = 1;
+            const unsigned nb = (unsigned)(((size_t)R * L.d.ff + 255) / 256);
+            if (m->f32) launch(m, lp_relu2_kernel<float>, dim3(nb), dim3(256), 0, (const float*)m->P + L.ff_off, L.n_in, (float*)m->act_a, L.d.ff, R);
+            else launch(m, lp_relu2_kernel<bf16>, dim3(nb), dim3(256), 0, (const float*)m->P + L.ff_off, L.n_in, (bf16*)m->act_a, L.d.ff, R);
             project_out(m->act_a, L.d.ff, L.w_down, L.norm2, nullptr);
         } else if (L.d.ff > 0) {
             sub = 1;

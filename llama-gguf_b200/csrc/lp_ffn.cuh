@@ -52,6 +52,16 @@ __global__ void lp_gated_gelu_kernel(const float* __restrict__ P, int ldp, OutT*
     out[i] = from_f<OutT>(gelu_tanh_f(p[n]) * p[ff + n]);
 }
 
+// out[r][n] = relu(P[r][n])^2 (the relu^2 layer when its up projection is part of a wider product)
+template <typename OutT>
+__global__ void lp_relu2_kernel(const float* __restrict__ P, int ldp, OutT* __restrict__ out, int ff, int R) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)R * ff) return;
+    const int r = (int)(i / ff), n = (int)(i - (size_t)r * ff);
+    const float z = fmaxf(P[(size_t)r * ldp + n], 0.0f);
+    out[i] = from_f<OutT>(z * z);
+}
+
 // Router: one warp per row of the f32 logits P[r][0 .. E) (route_row, lp_rows_tail.cuh)
 __global__ void lp_moe_route_kernel(const float* __restrict__ P, int ldp, int E, int top, float* __restrict__ wts, int* __restrict__ sel,
                                     float* __restrict__ selw, int R, int mode, float scale) {
@@ -67,28 +77,56 @@ __device__ __forceinline__ float expert_act(float z, int act) {
     return z * z;
 }
 
-// out[r][c] = act(P[r][off + c]) * (weight of the expert that owns column c; 1 for the always-on expert's columns behind them)
+// A gated expert (B200_ACT_SILU_GLU) has two pre-activations per hidden unit, silu(g) * u; its up matrix is [gate | up] rows.
+__device__ __forceinline__ int expert_rows(int eff, int act) { return act == B200_ACT_SILU_GLU ? 2 * eff : eff; }
+// hidden unit of an expert from its pre-activation(s) and the expert's weight w: on the output, act(.) w, or on the input (win),
+// where W (w h) = w (W h) puts it on the pre-activations
+__device__ __forceinline__ float expert_unit(float z, float zu, float w, int act, int win) {
+    if (win) { z *= w; zu *= w; }
+    const float v = act == B200_ACT_SILU_GLU ? z * sigmoid_f(z) * zu : expert_act(z, act);
+    return win ? v : v * w;
+}
+
+// out[r][c] = hidden unit c of the row: expert e = c / eff with its weight (0 = not chosen: the unit is 0), the always-on expert's
+// units behind them with weight 1.  P holds every expert's pre-activations side by side (expert_rows per expert).
 template <typename OutT>
 __global__ void lp_moe_act_kernel(const float* __restrict__ P, int ldp, int off, const float* __restrict__ wts, int E, int eff, int total,
-                                  OutT* __restrict__ out, int R, int act) {
+                                  OutT* __restrict__ out, int R, int act, int win) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (size_t)R * total) return;
     const int r = (int)(i / total), c = (int)(i - (size_t)r * total);
-    const int e = c / eff;
+    const int e = c / eff, per = expert_rows(eff, act);
     const float wgt = e < E ? wts[(size_t)r * E + e] : 1.0f;
     float v = 0.0f;
-    if (wgt != 0.0f) v = expert_act(P[(size_t)r * ldp + off + c], act) * wgt;
+    if (wgt != 0.0f) {
+        const float* p = P + (size_t)r * ldp + off;
+        if (e < E) v = expert_unit(p[e * per + (c - e * eff)], act == B200_ACT_SILU_GLU ? p[e * per + eff + (c - e * eff)] : 0.0f, wgt, act, win);
+        else v = expert_act(p[E * per + (c - E * eff)], act);
+    }
     out[i] = from_f<OutT>(v);
 }
 
-// Few rows (decoding): only the chosen experts' weights are read.  up_cat holds [router | e0 up | e1 up | ... | always-on up] rows of
-// `width` columns; segment k < top of a row's activations belongs to expert sel[r][k], segment `top` to the always-on expert.
-//   act[r][k eff + n] = act(up_e[n] . h_r) * selw[r][k]        act[r][top eff + n] = act(up_shared[n] . h_r),   act = relu^2 or GELU
+// The same for (token, choice) pairs in expert order: pair i = (row i / top, choice i % top) sits at row pos[i] of P (its expert's
+// pre-activations, expert_rows wide) and of out (eff wide); its weight is selw[i].
+template <typename OutT>
+__global__ void lp_moe_pair_act_kernel(const float* __restrict__ P, int ldp, const int* __restrict__ pos, const float* __restrict__ selw, int eff,
+                                       OutT* __restrict__ out, int n_pairs, int act, int win) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)n_pairs * eff) return;
+    const int pr = (int)(i / eff), n = (int)(i - (size_t)pr * eff);
+    const float* p = P + (size_t)pos[pr] * ldp;
+    out[(size_t)pos[pr] * eff + n] = from_f<OutT>(expert_unit(p[n], act == B200_ACT_SILU_GLU ? p[eff + n] : 0.0f, selw[pr], act, win));
+}
+
+// Few rows (decoding): only the chosen experts' weights are read.  up_exp holds [e0 up | e1 up | ... | always-on up] rows of `width`
+// columns (a gated expert: [gate | up], expert_rows each); segment k < top of a row's activations belongs to expert sel[r][k],
+// segment `top` to the always-on expert.
+//   act[r][k eff + n] = unit(up_e[n] . h_r, selw[r][k])        act[r][top eff + n] = act(up_shared[n] . h_r)      (expert_unit)
 // One warp per (row, segment, n); h rows are staged in shared memory once per block.
 template <typename T>
-__global__ void __launch_bounds__(256) lp_moe_up_sel_kernel(const T* __restrict__ H, const T* __restrict__ up_cat, const int* __restrict__ sel,
+__global__ void __launch_bounds__(256) lp_moe_up_sel_kernel(const T* __restrict__ H, const T* __restrict__ up_exp, const int* __restrict__ sel,
                                                             const float* __restrict__ selw, int E, int top, int eff, int sff, int width, int R,
-                                                            T* __restrict__ act, int act_kind) {
+                                                            T* __restrict__ act, int act_kind, int win) {
     extern __shared__ __align__(16) uint8_t mu_smem[];
     T* hs = reinterpret_cast<T*>(mu_smem);
     constexpr int VN = Vec8<T>::N;
@@ -103,28 +141,37 @@ __global__ void __launch_bounds__(256) lp_moe_up_sel_kernel(const T* __restrict_
         const int k = c < top * eff ? c / eff : top;
         const int n = c - k * eff;
         const int e = k < top ? sel[(size_t)r * top + k] : E;
-        const T* wr = up_cat + ((size_t)E + (size_t)e * eff + n) * width;
+        const int per = expert_rows(eff, act_kind);
+        const bool glu = act_kind == B200_ACT_SILU_GLU && k < top;
+        const T* wr = up_exp + ((size_t)e * per + n) * width;
+        const T* wu = wr + (size_t)eff * width;          // (gated experts: the up row of the same unit)
         const T* hr = hs + (size_t)r * width;
-        float acc = 0.0f;
+        float acc = 0.0f, accu = 0.0f;
         for (int i = lane * VN; i < width; i += 32 * VN) {
             float wv[VN], xv[VN];
             Vec8<T>::load(wr + i, wv);
             Vec8<T>::load(hr + i, xv);
 #pragma unroll
             for (int j = 0; j < VN; j++) acc = fmaf(wv[j], xv[j], acc);
+            if (glu) {
+                Vec8<T>::load(wu + i, wv);
+#pragma unroll
+                for (int j = 0; j < VN; j++) accu = fmaf(wv[j], xv[j], accu);
+            }
         }
         acc = wsum(acc);
-        if (lane == 0) act[o] = from_f<T>(expert_act(acc, act_kind) * (k < top ? selw[(size_t)r * top + k] : 1.0f));
+        accu = wsum(accu);
+        if (lane == 0) act[o] = from_f<T>(k < top ? expert_unit(acc, accu, selw[(size_t)r * top + k], act_kind, win) : expert_act(acc, act_kind));
     }
 }
 
 // y[r][c] = sum over the row's segments of down_e[c] . act segment; down_cat is [width][E eff + sff].  MD_SPLIT warps share one (row, c):
 // each takes every MD_SPLIT-th 16-byte group of every segment (more loads in flight per output: a decode step has only `width` of
-// them), the partial sums meet in shared memory and are added in warp order.
+// them), the partial sums meet in shared memory and are added in warp order.  accum = 1: y += (y is the residual stream).
 constexpr int MD_SPLIT = 4;
 template <typename T>
 __global__ void __launch_bounds__(256) lp_moe_down_sel_kernel(const T* __restrict__ act, const T* __restrict__ down_cat, const int* __restrict__ sel,
-                                                              int E, int top, int eff, int sff, int width, int R, float* __restrict__ y, RowsTail tail) {
+                                                              int E, int top, int eff, int sff, int width, int R, float* __restrict__ y, RowsTail tail, int accum) {
     constexpr int VN = Vec8<T>::N, GROUPS = 8 / MD_SPLIT;
     __shared__ float part[8];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, grp = warp / MD_SPLIT, sw = warp % MD_SPLIT;
@@ -158,7 +205,7 @@ __global__ void __launch_bounds__(256) lp_moe_down_sel_kernel(const T* __restric
             float t = part[grp * MD_SPLIT];
 #pragma unroll
             for (int i = 1; i < MD_SPLIT; i++) t += part[grp * MD_SPLIT + i];
-            y[o] = t;
+            y[o] = accum ? y[o] + t : t;
         }
         __syncthreads();
     }
@@ -203,15 +250,15 @@ __global__ void lp_moe_gather_kernel(const T* __restrict__ H, const int* __restr
     }
 }
 
-// y[r] (+)= sum_k selw[r][k] Yp[pos[r top + k]], choices in the order they were taken; add = 1 when y already holds the always-on
-// expert's output
+// y[r] (+)= sum_k selw[r][k] Yp[pos[r top + k]], choices in the order they were taken; add = 1 when y already holds something to add
+// to (the always-on expert's output, or the residual stream); selw = null: plain sum (the weights went into the experts' inputs)
 __global__ void lp_moe_combine_kernel(const float* __restrict__ Yp, const int* __restrict__ pos, const float* __restrict__ selw, int top, int width,
                                       int add, float* __restrict__ y) {
     const int r = blockIdx.x;
     for (int c = threadIdx.x; c < width; c += blockDim.x) {
-        float acc = add ? y[(size_t)r * width + c] : 0.0f;
-        for (int k = 0; k < top; k++) acc = fmaf(selw[(size_t)r * top + k], Yp[(size_t)pos[(size_t)r * top + k] * width + c], acc);
-        y[(size_t)r * width + c] = acc;
+        float acc = add ? y[(size_t)r * width + c] : 0.0f, sum = 0.0f;
+        for (int k = 0; k < top; k++) sum = fmaf(selw ? selw[(size_t)r * top + k] : 1.0f, Yp[(size_t)pos[(size_t)r * top + k] * width + c], sum);
+        y[(size_t)r * width + c] = acc + sum;
     }
 }
 

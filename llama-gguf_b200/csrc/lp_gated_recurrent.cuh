@@ -1,0 +1,181 @@
+// lp_gated_recurrent.cuh — the recurrent branches of B200_MIX_ATTN_RECURRENT (a softmax mixer beside a recurrent unit on the same
+// normed input), how the two branches meet, and the clamped gated feed-forward.  Included by layerprog.cu inside its anonymous
+// namespace (after the scan helpers of the matrix memory).  Gates, states and norms are f32 in both compute modes.
+#pragma once
+
+// ------------------------------------------------------------------------------------------------ gated linear memory
+// Per (run, head): S [dim][vdim] f32.  With q = silu(zq), f = l + (1 - l) sigmoid(zf + b) per key channel:
+//   S <- diag(f) S + (1 - f) v^T,   o = S^T q          (the forget gate also says how much of v is written).
+// Laid out like the library's other scans: thread column j of S, the column cut into 16-channel pieces over neighbouring lanes,
+// tokens staged a chunk at a time, gates worked out once per (token, channel) in shared memory before the serial loop.
+// State block of a run: S [H][dim][vdim].
+struct GlinGeom {
+    int H, dim, vdim;
+    int q_off, v_off, f_off;   // columns of P
+    size_t rec_off;
+};
+template <int DMAX>
+__global__ void __launch_bounds__(SCAN_BD) lp_gated_linear_kernel(StepMeta sm, GlinGeom g, const float* __restrict__ P, int ldp,
+                                                                  const float* __restrict__ fb, const float* __restrict__ lower,
+                                                                  float* __restrict__ O, int ldo) {
+    constexpr int CH = ScanChunk<DMAX>::N, SPLIT = DMAX / SCAN_DREG, COLS = SCAN_BD / SPLIT;
+    __shared__ __align__(16) float qs[CH][DMAX];
+    __shared__ __align__(16) float fs[CH][DMAX];
+    __shared__ float vs[CH][COLS];
+    const int tid = threadIdx.x, col = tid / SPLIT, sub = tid % SPLIT;
+    const int j = blockIdx.x * COLS + col, h = blockIdx.y, run = blockIdx.z;
+    const int r0 = sm.run_start[run], r1 = sm.run_start[run + 1];
+    float* Sg = reinterpret_cast<float*>(sm.run_rec[run] + g.rec_off) + (size_t)h * g.dim * g.vdim;
+    const bool live = j < g.vdim;
+    float s[SCAN_DREG];
+#pragma unroll
+    for (int i = 0; i < SCAN_DREG; i++) {
+        const int d = ((i >> 2) * SPLIT + sub) * 4 + (i & 3);   // channel of register i
+        s[i] = (live && d < g.dim) ? Sg[(size_t)d * g.vdim + j] : 0.0f;
+    }
+    for (int i = tid; i < CH * DMAX; i += SCAN_BD) {   // beyond dim: q = 0 and f = 1, so the padding rows stay zero
+        (&qs[0][0])[i] = 0.0f;
+        (&fs[0][0])[i] = 1.0f;
+    }
+    const int jc = blockIdx.x * COLS + (tid % COLS);   // the column this thread stages
+    for (int c0 = r0; c0 < r1; c0 += CH) {
+        const int nt = min(CH, r1 - c0);
+        __syncthreads();   // the previous chunk has been consumed
+        for (int t = 0; t < nt; t++) {
+            const float* p = P + (size_t)(c0 + t) * ldp;
+            for (int d = tid; d < g.dim; d += SCAN_BD) {
+                cp_async4(&qs[t][d], p + g.q_off + h * g.dim + d);
+                cp_async4(&fs[t][d], p + g.f_off + h * g.dim + d);
+            }
+        }
+        for (int t = tid / COLS; t < nt; t += SPLIT) {
+            if (jc < g.vdim) cp_async4(&vs[t][tid % COLS], P + (size_t)(c0 + t) * ldp + g.v_off + h * g.vdim + jc);
+            else vs[t][tid % COLS] = 0.0f;
+        }
+        cp_async_wait_all();   // (a thread turns the pre-activations it has copied itself)
+        for (int t = 0; t < nt; t++)
+            for (int d = tid; d < g.dim; d += SCAN_BD) {
+                const float zq = qs[t][d], lo = lower[h * g.dim + d];
+                qs[t][d] = zq * sigmoid_f(zq);
+                fs[t][d] = lo + (1.0f - lo) * sigmoid_f(fs[t][d] + fb[h * g.dim + d]);
+            }
+        __syncthreads();
+        for (int t = 0; t < nt; t++) {
+            const float v = vs[t][col];
+            float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+#pragma unroll
+            for (int i = 0; i < SCAN_DREG; i += 4) {
+                const float4 f4 = *reinterpret_cast<const float4*>(&fs[t][((i >> 2) * SPLIT + sub) * 4]);
+                const float4 q4 = *reinterpret_cast<const float4*>(&qs[t][((i >> 2) * SPLIT + sub) * 4]);
+                s[i] = fmaf(f4.x, s[i] - v, v);
+                s[i + 1] = fmaf(f4.y, s[i + 1] - v, v);
+                s[i + 2] = fmaf(f4.z, s[i + 2] - v, v);
+                s[i + 3] = fmaf(f4.w, s[i + 3] - v, v);
+                a0 = fmaf(s[i], q4.x, a0);
+                a1 = fmaf(s[i + 1], q4.y, a1);
+                a2 = fmaf(s[i + 2], q4.z, a2);
+                a3 = fmaf(s[i + 3], q4.w, a3);
+            }
+            const float acc = split_sum<SPLIT>((a0 + a1) + (a2 + a3));
+            if (live && sub == 0) O[(size_t)(c0 + t) * ldo + h * g.vdim + j] = acc;
+        }
+    }
+    if (live)
+#pragma unroll
+        for (int i = 0; i < SCAN_DREG; i++) {
+            const int d = ((i >> 2) * SPLIT + sub) * 4 + (i & 3);
+            if (d < g.dim) Sg[(size_t)d * g.vdim + j] = s[i];
+        }
+}
+
+// ------------------------------------------------------------------------------------------------ gated unit
+// One state per channel: z = sigmoid(zz + bz), u = zx + bx, c = u + 1/2 (u >= 0) or sigmoid(u) (u < 0), s <- (1 - z) s + z c;
+// out = s * silu(zg) * out_scale in the compute type (the operand of the branch's output projection).  State block of a run: s [width].
+// s_t = a_t s_(t-1) + b_t with a = 1 - z, b = z c is a composition of affine maps, so a run is cut into GU_SEG segments that
+// blockDim.y threads per channel fold on their own (A = prod a, B = the segment's s from s = 0); the carries are then chained in
+// shared memory and every segment is walked once more from its true start.  One token per run (decoding) is one segment.
+struct GunitGeom {
+    int width;
+    int z_off, x_off, g_off;   // columns of P
+    size_t rec_off;
+};
+constexpr int GU_CH = 32, GU_SEG = 8;   // channels and segments per block
+__device__ __forceinline__ void gunit_ab(const float* __restrict__ p, const GunitGeom& g, int c, float bz, float bx, float& a, float& b) {
+    const float z = sigmoid_f(p[g.z_off + c] + bz), u = p[g.x_off + c] + bx;
+    const float cand = u >= 0.0f ? u + 0.5f : sigmoid_f(u);
+    a = 1.0f - z;
+    b = z * cand;
+}
+template <typename OutT>
+__global__ void __launch_bounds__(GU_CH * GU_SEG) lp_gated_unit_kernel(StepMeta sm, GunitGeom g, const float* __restrict__ P, int ldp,
+                                                                        const float* __restrict__ zb, const float* __restrict__ xb,
+                                                                        OutT* __restrict__ out, int out_ld, float out_scale) {
+    __shared__ float As[GU_SEG][GU_CH], Bs[GU_SEG][GU_CH];
+    const int c = blockIdx.x * GU_CH + threadIdx.x, seg = threadIdx.y, run = blockIdx.y;
+    const int r0 = sm.run_start[run], len = sm.run_start[run + 1] - r0;
+    float* sg = reinterpret_cast<float*>(sm.run_rec[run] + g.rec_off);
+    const bool live = c < g.width;
+    const int per = (len + GU_SEG - 1) / GU_SEG;
+    const int t0 = min(seg * per, len), t1 = min(t0 + per, len);
+    const float bz = live ? zb[c] : 0.0f, bx = live ? xb[c] : 0.0f;
+    float A = 1.0f, B = 0.0f;
+    if (live && len > per)   // (a single segment needs no first pass)
+        for (int t = t0; t < t1; t++) {
+            float a, b;
+            gunit_ab(P + (size_t)(r0 + t) * ldp, g, c, bz, bx, a, b);
+            A *= a;
+            B = fmaf(a, B, b);
+        }
+    As[seg][threadIdx.x] = A;
+    Bs[seg][threadIdx.x] = B;
+    float s = live ? sg[c] : 0.0f;   // (read before the barrier: the last segment's thread overwrites it after its walk)
+    __syncthreads();
+    for (int q = 0; q < seg; q++) s = fmaf(As[q][threadIdx.x], s, Bs[q][threadIdx.x]);   // the state at the start of this segment
+    if (!live) return;
+    for (int t = t0; t < t1; t++) {
+        const float* p = P + (size_t)(r0 + t) * ldp;
+        float a, b;
+        gunit_ab(p, g, c, bz, bx, a, b);
+        s = fmaf(a, s, b);
+        const float zg = p[g.g_off + c];
+        out[(size_t)(r0 + t) * out_ld + c] = from_f<OutT>(s * zg * sigmoid_f(zg) * out_scale);
+    }
+    if (seg == (len - 1) / per) sg[c] = s;   // the last segment that holds tokens ends on the run's last state
+}
+
+// ------------------------------------------------------------------------------------------------ how the branches meet
+// x[r] += weight * (a / rms(a) * wa + b / rms(b) * wb), a = ya[r], b = yb[r] the two branches' projected outputs; one block per row.
+__global__ void __launch_bounds__(256) lp_dual_norm_add_kernel(float* __restrict__ x, const float* __restrict__ ya, const float* __restrict__ yb, int ldy,
+                                                               const float* __restrict__ wa, const float* __restrict__ wb, int width, float eps,
+                                                               float weight) {
+    __shared__ float red[2][8];
+    const int r = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const float* a = ya + (size_t)r * ldy;
+    const float* b = yb + (size_t)r * ldy;
+    float sa = 0.0f, sb = 0.0f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        sa = fmaf(a[c], a[c], sa);
+        sb = fmaf(b[c], b[c], sb);
+    }
+    sa = wsum(sa);
+    sb = wsum(sb);
+    if (lane == 0) { red[0][warp] = sa; red[1][warp] = sb; }
+    __syncthreads();
+    sa = 0.0f; sb = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) { sa += red[0][i]; sb += red[1][i]; }
+    const float ia = 1.0f / sqrtf(sa / (float)width + eps), ib = 1.0f / sqrtf(sb / (float)width + eps);
+    for (int c = threadIdx.x; c < width; c += blockDim.x) x[(size_t)r * width + c] += weight * (a[c] * ia * wa[c] + b[c] * ib * wb[c]);
+}
+
+// ------------------------------------------------------------------------------------------------ clamped gated feed-forward
+// out[r][n] = g sigmoid(slope g) (u + 1), g = min(P[r][n], limit), u = clamp(P[r][ff + n], -limit, limit): P holds [gate | up]
+template <typename OutT>
+__global__ void lp_clamped_glu_kernel(const float* __restrict__ P, int ldp, OutT* __restrict__ out, int ff, int R, float limit, float slope) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)R * ff) return;
+    const int r = (int)(i / ff), n = (int)(i - (size_t)r * ff);
+    const float* p = P + (size_t)r * ldp;
+    const float g = fminf(p[n], limit), u = fminf(fmaxf(p[ff + n], -limit), limit);
+    out[i] = from_f<OutT>(g * sigmoid_f(slope * g) * (u + 1.0f));
+}

@@ -6,7 +6,8 @@
 
 // Router of a mixture of experts for one row, by one warp: the `top` largest of z[0 .. E) are taken one after the other (of equal
 // logits the lower index first); their weights are the softmax over the chosen logits only (mode B200_ROUTE_TOP_SOFTMAX), or their
-// share of the softmax over ALL experts times `scale`, not renormalised (B200_ROUTE_SOFTMAX_TOP).  w[e] receives the weight of
+// share of the softmax over ALL experts times `scale`, not renormalised (B200_ROUTE_SOFTMAX_TOP), or their own sigmoid, not
+// renormalised, times `scale` when that is not 0 (B200_ROUTE_SIGMOID_TOP).  w[e] receives the weight of
 // expert e (0 when it is not chosen); sel[k] / selw[k] list the chosen experts in the order they were taken.
 __device__ __forceinline__ void route_row(const float* __restrict__ z, int E, int top, float* __restrict__ w, int* __restrict__ sel,
                                           float* __restrict__ selw, int lane, int mode, float scale) {
@@ -35,7 +36,7 @@ __device__ __forceinline__ void route_row(const float* __restrict__ z, int E, in
             if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
         }
         if (k == 0) zmax = best;
-        const float p = expf(best - zmax);
+        const float p = mode == B200_ROUTE_SIGMOID_TOP ? sigmoid_f(best) : expf(best - zmax);
         sum += p;
         if (lane == 0) {
             w[bi] = -1.0f - p;          // mark; turned into the weight below
@@ -44,7 +45,7 @@ __device__ __forceinline__ void route_row(const float* __restrict__ z, int E, in
         }
         __syncwarp();
     }
-    const float inv = mode == B200_ROUTE_SOFTMAX_TOP ? scale / all : 1.0f / sum;
+    const float inv = mode == B200_ROUTE_SIGMOID_TOP ? (scale != 0.0f ? scale : 1.0f) : mode == B200_ROUTE_SOFTMAX_TOP ? scale / all : 1.0f / sum;
     for (int e = lane; e < E; e += 32)
         if (w[e] != 0.0f) w[e] = (-1.0f - w[e]) * inv;
     for (int k = lane; k < top; k += 32) selw[k] *= inv;

@@ -14,22 +14,29 @@ struct PrepGeom {
     int rot_dims;          // 0: no rotation
     int v_mix;             // B200_VMIX_*
     size_t rec_off;
+    int rot_after_norm;    // 1: the q / k norm first, then the rotation
+    float rot_gain;        // factor on cos and sin of the q / k rotation (stretched frequencies), 1 otherwise
+    int v_rot;             // 1: the values are turned by their position (all pairs of a head, frequencies v_freq) before they are cached
 };
 
 // One block per row.  Step 1: u = P + bias, y = causal convolution of u over time (inputs before the run's first row come from the
 // run's tail, zeros at the start of a sequence) into shared memory.  Step 2: per head of q and k (a warp each): rotate the first
 // rot_dims channels (channel 2i with 2i + 1).  Step 3: the norm (over the whole of q and of k, or a warp per head).  Step 4: q to
 // qbuf, k to the cache row, v (blended) to the cache row.  shift_tail: the step has one row per run and the block also moves the
-// run's tail on by this row (else lp_attn_conv_tail_kernel does it for the whole run afterwards).
+// run's tail on by this row (else lp_attn_conv_tail_kernel does it for the whole run afterwards).  rot_after_norm swaps steps 2 and 3.
+// v_rot: the pairs (2m, 2m + 1) of every value head are turned by pos * v_freq[m]; cos | sin of these angles also go to
+// vrot_out[r][vdim], where the attention kernels find them to turn the summed values back.
 __global__ void __launch_bounds__(256) lp_attn_prep2_kernel(StepMeta sm, AttnGeom a, PrepGeom g, const float* __restrict__ P, int ldp,
                                                             const float* __restrict__ bias, const float* __restrict__ cw,
                                                             const float* __restrict__ qw, const float* __restrict__ kw,
                                                             const double* __restrict__ inv_freq, const float* __restrict__ lam_p,
-                                                            float* __restrict__ vsrc, float* __restrict__ qbuf, int shift_tail) {
+                                                            float* __restrict__ vsrc, float* __restrict__ qbuf, int shift_tail,
+                                                            const double* __restrict__ v_freq, float* __restrict__ vrot_out) {
     extern __shared__ __align__(16) float ps[];
     float* y = ps;                              // [C]
     float* cs = ps + ((g.C + 3) & ~3);          // [rot_dims / 2] cos, then sin
     float* sn = cs + g.rot_dims / 2;
+    float* vcs = cs + g.rot_dims;               // [vdim / 2] cos, then sin (v_rot)
     __shared__ float red[2][8];
     const int r = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     const int run = sm.row_run[r], pos = sm.row_pos[r], t = r - sm.run_start[run];
@@ -56,12 +63,22 @@ __global__ void __launch_bounds__(256) lp_attn_prep2_kernel(StepMeta sm, AttnGeo
     for (int i = threadIdx.x; i < g.rot_dims / 2; i += blockDim.x) {
         double s, c;
         sincos((double)pos * inv_freq[i], &s, &c);
-        cs[i] = (float)c;
-        sn[i] = (float)s;
+        cs[i] = (float)c * g.rot_gain;
+        sn[i] = (float)s * g.rot_gain;
+    }
+    if (g.v_rot) {
+        for (int i = threadIdx.x; i < a.vdim / 2; i += blockDim.x) {
+            double s, c;
+            sincos((double)pos * v_freq[i], &s, &c);
+            vcs[i] = (float)c;
+            vcs[a.vdim / 2 + i] = (float)s;
+            vrot_out[(size_t)r * a.vdim + i] = (float)c;
+            vrot_out[(size_t)r * a.vdim + a.vdim / 2 + i] = (float)s;
+        }
     }
     __syncthreads();
     const int nq = a.H * a.dim, nk = a.G * a.dim;
-    if (g.rot_dims > 0) {
+    auto rotate_qk = [&]() {
         for (int h = warp; h < a.H + a.G; h += nw) {
             float* v = y + h * a.dim;
             for (int i = lane; i < g.rot_dims / 2; i += 32) {
@@ -71,7 +88,8 @@ __global__ void __launch_bounds__(256) lp_attn_prep2_kernel(StepMeta sm, AttnGeo
             }
         }
         __syncthreads();
-    }
+    };
+    if (g.rot_dims > 0 && !g.rot_after_norm) rotate_qk();
     if (g.qk_norm == B200_QKNORM_WHOLE_WEIGHT) {   // one root mean square over all of q, one over all of k
         float sq = 0.0f, sk = 0.0f;
         for (int c = threadIdx.x; c < nq; c += blockDim.x) sq += y[c] * y[c];
@@ -97,6 +115,18 @@ __global__ void __launch_bounds__(256) lp_attn_prep2_kernel(StepMeta sm, AttnGeo
         }
     }
     __syncthreads();
+    if (g.rot_dims > 0 && g.rot_after_norm) rotate_qk();
+    if (g.v_rot) {
+        const int half = a.vdim / 2;
+        for (int i = threadIdx.x; i < a.G * half; i += blockDim.x) {
+            const int hv = i / half, pm = i - hv * half;
+            float* v = y + nq + nk + hv * a.vdim;
+            const float u0 = v[2 * pm], u1 = v[2 * pm + 1];
+            v[2 * pm] = u0 * vcs[pm] - u1 * vcs[half + pm];
+            v[2 * pm + 1] = u1 * vcs[pm] + u0 * vcs[half + pm];
+        }
+        __syncthreads();
+    }
     float* kc = reinterpret_cast<float*>(sm.run_kv[run] + a.kv_off) + (size_t)pos * nk;
     float* vc = reinterpret_cast<float*>(sm.run_kv[run] + a.kv_off) + (size_t)a.cap * nk + (size_t)pos * a.G * a.vdim;
     for (int c = threadIdx.x; c < nq; c += blockDim.x) qbuf[(size_t)r * nq + c] = y[c];

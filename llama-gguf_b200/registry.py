@@ -24,7 +24,12 @@ def _madudra(path, **kw):
     return madudra.load(path, **kw)
 
 
-LOADERS = {"Lazilorn": _lazilorn, "Mefurax": _mefurax, "Madudra": _madudra}
+def _marosun(path, **kw):
+    from . import marosun
+    return marosun.load(path, **kw)
+
+
+LOADERS = {"Lazilorn": _lazilorn, "Mefurax": _mefurax, "Madudra": _madudra, "Marosun": _marosun}
 
 
 def architecture_of(path):
