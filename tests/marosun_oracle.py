@@ -219,7 +219,7 @@ class Model:
         self.eps = float(cfg["norm"]["eps"])
 
     def new_state(self):
-        return [{"cache": [], "right": {}} for _ in self.cfg["layers"]]
+        return {"n": 0, "layers": [{"cache": [], "right": {}} for _ in self.cfg["layers"]]}
 
     def mixer(self, i, L, h, t, st):
         pre, m, kind = "l%d.mix." % i, L["mixer"], L["type"]
@@ -242,20 +242,25 @@ class Model:
             return dense_ff(h, self.w[pre + "gate"], self.w[pre + "up"], self.w[pre + "down"], float(mlp["limit"]))
         return mixture_ff(h, self.w, pre, mlp["router"]["experts"], mlp["router"]["top"])
 
-    def token(self, tok, t, state, taps=None):
+    def token(self, tok, state, taps=None):
+        t = state["n"]
         x = self.w["embed"][tok].copy()
         for i, L in enumerate(self.cfg["layers"]):
             h = offset_norm(x, self.w["l%d.norm1" % i], self.eps)
-            x = x + (self.mixer(i, L, h, t, state[i]) + self.ff(i, L, h))
+            x = x + (self.mixer(i, L, h, t, state["layers"][i]) + self.ff(i, L, h))
             if taps is not None:
                 taps[i].append(x.copy())
+        state["n"] = t + 1
         return self.w["head"] @ offset_norm(x, self.w["final.norm"], self.eps)
 
-    def forward(self, tokens, taps_out=None, state=None, pos0=0):
-        """logits [len(tokens), vocab]; taps_out (a list) receives the residual stream after every layer, [layers][tokens, width]."""
-        state = state if state is not None else self.new_state()
+    def step(self, state, tokens, taps_out=None):
+        """the next tokens of the sequence that `state` holds -> logits [len(tokens), vocab]; taps_out (a list) receives the residual
+        stream after every layer, [layers][tokens, width]"""
         taps = [[] for _ in self.cfg["layers"]] if taps_out is not None else None
-        out = [self.token(tok, pos0 + j, state, taps) for j, tok in enumerate(tokens)]
+        out = [self.token(tok, state, taps) for tok in tokens]
         if taps_out is not None:
             taps_out.extend(np.stack(a) for a in taps)
         return np.stack(out)
+
+    def forward(self, tokens, taps_out=None):
+        return self.step(self.new_state(), tokens, taps_out)
