@@ -192,7 +192,7 @@ def main():
     ap.add_argument("--no-speculation", action="store_true", help="e2e: only the plain b200_forward loop (no greedy continuation)")
     ap.add_argument("--kv-format", default=os.environ.get("B200_KV_FORMAT", "f32"), choices=["f32", "int8"],
                     help="KV cache storage (SURVEY 8f row 4): int8 = QuantizedKVCache Int8 rows + one scale per row (per-op decode path)")
-    ap.add_argument("--design", default=None, choices=["lazilorn", "mefurax", "madudra"],
+    ap.add_argument("--design", default=None, choices=["lazilorn", "mefurax", "madudra", "marosun"],
                     help="instead of the default workload: prefill / decode throughput of this layer-program design at a few sizes, "
                          "beside a llama-architecture model of the same size (bench_layers.py)")
     ap.add_argument("--sizes", default="", help="--design: comma-separated size names (default: all)")

@@ -1,8 +1,9 @@
-"""bench.py --design lazilorn | mefurax | madudra: prefill and decode throughput of a layer-program design at sizes that resemble a real model's
+"""bench.py --design lazilorn | mefurax | madudra | marosun: prefill and decode throughput of a layer-program design at sizes that resemble a real model's
 layers (random weights), beside the library's closest existing model -- a llama-architecture transformer of the same width, depth
 and parameter count in Q8_0 blocks (the densest weight type its tensor-core prompt path takes); Mefurax also beside Lazilorn at
 the same width and depth (the other bf16 layer program, whose attention and GEMM kernels it shares); Madudra beside Lazilorn (the
-other hybrid of attention and recurrent scans) and Mefurax (the other mixture of experts) at the same width and depth.
+other hybrid of attention and recurrent scans) and Mefurax (the other mixture of experts) at the same width and depth; Marosun beside
+the same two (Lazilorn: attention beside a matrix memory; Mefurax: softmax mixers with rotation and experts).
 
 Per size and model: prompt tokens/s for one prompt of --prefill-len tokens, decode tokens/s at batch 1 and at --batch sequences
 after prompts of --prompt-len tokens.  Every number is host wall clock around the library call (each call ends with a stream
@@ -85,6 +86,35 @@ def madudra_config(s, span=1024):
             "residual_mult": 0.5, "streams": s["streams"], "layers": layers}
 
 
+MAROSUN_SIZES = {
+    # name: width, layers (a = attention with turned values, q = attention beside a gated unit, p = chunked attention beside a gated linear
+    # memory; D = dense clamped feed-forward, M = mixture of gated experts), heads / kv heads, dense ff, experts / chosen / expert ff
+    "w1024": dict(width=1024, pattern=["aD", "aM", "qD", "pM", "aD", "pM"], heads=8, kv_heads=2, ff=4096, experts=8, top=2, eff=1024, vocab=32000),
+    "w2048": dict(width=2048, pattern=["aD", "aM", "qD", "pM", "aD", "aM", "qD", "pM"], heads=16, kv_heads=4, ff=8192, experts=8, top=2, eff=2048,
+                  vocab=32000),
+}
+
+
+def marosun_config(s, span=1024):
+    # heads of 128 key and 128 value channels; the memory branch has as many heads of 128 x 128 state; the gated unit is twice the width
+    layers = []
+    rot = {"dims": 64, "base": 10000.0, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
+    for ch, ff in s["pattern"]:
+        mlp = {"kind": "dense", "ff": s["ff"], "limit": 7.0} if ff == "D" else {"kind": "moe", "router": {"experts": s["experts"], "top": s["top"]},
+                                                                                "expert": {"ff": s["eff"]}}
+        soft = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": 128, "vdim": 128, "scale": 128 ** -0.5}
+        if ch == "a":
+            layers.append({"type": "attention", "mixer": dict(soft, rot=rot), "mlp": mlp})
+        elif ch == "q":
+            layers.append({"type": "parallel_2", "mlp": mlp,
+                           "mixer": {"left": dict(soft, rot={"dims": 128, "base": 10000.0}), "right": {"width": 2 * s["width"]}}})
+        else:
+            layers.append({"type": "parallel", "mlp": mlp,
+                           "mixer": {"left": dict(soft, mask={"size": span}), "right": {"heads": s["heads"], "dim": 128, "vdim": 128},
+                                     "left_scale": 0.7, "right_scale": 0.7}})
+    return {"architecture": "Marosun", "width": s["width"], "vocab": s["vocab"], "norm": {"eps": 1e-6}, "layers": layers}
+
+
 def lazilorn_feeder(cfg, seed, tensor_shapes=None):
     """upload(name, type, ne, data) for every tensor of cfg: bf16 bit patterns of N(0, 1/fan_in) matrices, f32 vectors."""
     import llama_gguf_b200 as B
@@ -109,9 +139,11 @@ def lazilorn_feeder(cfg, seed, tensor_shapes=None):
                 a = 0.5 * rng.standard_normal(shape)
             elif name.endswith("f.b"):
                 a = rng.uniform(1.0, 4.0, shape)
+            elif last == "lower":
+                a = rng.uniform(0.0, 0.9, shape)
             elif last in ("A_log", "dt_bias", "b") and len(shape) == 1:
                 a = rng.uniform(-2.0, 0.5, shape)
-            elif last in ("norm1", "norm2", "vmix") and cfg["architecture"] == "Mefurax" or (name == "final.norm" and cfg["architecture"] == "Mefurax"):
+            elif (last in ("norm1", "norm2", "vmix") or name == "final.norm") and cfg["architecture"] in ("Mefurax", "Marosun"):
                 a = 0.1 * rng.standard_normal(shape) + (0.4 if last == "vmix" else 0.0)
             else:
                 a = 1.0 + 0.1 * rng.standard_normal(shape)
@@ -120,8 +152,8 @@ def lazilorn_feeder(cfg, seed, tensor_shapes=None):
 
 
 def design_module(cfg):
-    from llama_gguf_b200 import lazilorn, madudra, mefurax
-    return {"Lazilorn": lazilorn, "Mefurax": mefurax, "Madudra": madudra}[cfg["architecture"]]
+    from llama_gguf_b200 import lazilorn, madudra, marosun, mefurax
+    return {"Lazilorn": lazilorn, "Mefurax": mefurax, "Madudra": madudra, "Marosun": marosun}[cfg["architecture"]]
 
 
 def n_params(cfg):
@@ -213,6 +245,8 @@ def main(args):
         return main_mefurax(args)
     if args.design == "madudra":
         return main_madudra(args)
+    if args.design == "marosun":
+        return main_marosun(args)
     sizes = [x for x in (args.sizes.split(",") if args.sizes else SIZES) if x]
     max_seq = max(args.prefill_len, args.prompt_len + args.warmup + args.steps + 8) + 8
     res = {}
@@ -279,4 +313,27 @@ def main_madudra(args):
     print(json.dumps({"bench": "design", "design": "madudra", "unit": "tok/s", "prefill_len": args.prefill_len, "prompt_len": args.prompt_len,
                       "batch": args.batch, "steps": args.steps, "warmup": args.warmup, "timing": "host wall clock around the library calls",
                       "dtype": "bf16 (madudra, lazilorn, mefurax at the same width and depth)", "data": "synthetic", "sizes": res}))
+    return 0
+
+
+def main_marosun(args):
+    sizes = [x for x in (args.sizes.split(",") if args.sizes else MAROSUN_SIZES) if x]
+    max_seq = max(args.prefill_len, args.prompt_len + args.warmup + args.steps + 8) + 8
+    res = {}
+    for name in sizes:
+        s = MAROSUN_SIZES[name]
+        cfg = marosun_config(s)
+        params = n_params(cfg)
+        n_moe = sum(1 for p in s["pattern"] if p[1] == "M")
+        active = params - n_moe * (s["experts"] - s["top"]) * 3 * s["width"] * s["eff"]
+        r = {"params_without_embedding": params, "active_params_without_embedding": active, "layers": ",".join(s["pattern"]),
+             "marosun_bf16": bench_lazilorn(cfg, args, max_seq)}
+        print(name, json.dumps(r), file=sys.stderr, flush=True)
+        r["lazilorn_bf16"] = bench_lazilorn(lazilorn_config(SIZES[name]), args, max_seq)
+        r["mefurax_bf16"] = bench_lazilorn(mefurax_config(MEFURAX_SIZES[name]), args, max_seq)
+        res[name] = r
+        print(name, json.dumps(r), file=sys.stderr, flush=True)
+    print(json.dumps({"bench": "design", "design": "marosun", "unit": "tok/s", "prefill_len": args.prefill_len, "prompt_len": args.prompt_len,
+                      "batch": args.batch, "steps": args.steps, "warmup": args.warmup, "timing": "host wall clock around the library calls",
+                      "dtype": "bf16 (marosun, lazilorn, mefurax at the same width and depth)", "data": "synthetic", "sizes": res}))
     return 0
