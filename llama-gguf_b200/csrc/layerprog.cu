@@ -2756,7 +2756,9 @@ void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want,
                     const int ldo = gg.H * gg.vdim;
                     const int cols = SCAN_BD / (pick_dmax(gg.dim) / SCAN_DREG);
                     dim3 sgrid((gg.vdim + cols - 1) / cols, gg.H, n_runs);
-#define LP_GLIN(DM) launch(m, lp_gated_linear_kernel<DM>, sgrid, dim3(SCAN_BD), 0, sm, gg, (const float*)m->P, L.n_in, L.rec_b0, L.rec_lower, m->O, ldo)
+                    const int vec4 = (gg.dim % 4 == 0 && gg.q_off % 4 == 0 && gg.f_off % 4 == 0 && L.n_in % 4 == 0) ? 1 : 0;
+                    launch(m, lp_glin_gates_kernel, dim3((unsigned)(((size_t)R * gg.H * gg.dim + 255) / 256)), dim3(256), 0, m->P, L.n_in, gg, L.rec_b0, L.rec_lower, R);
+#define LP_GLIN(DM) launch(m, lp_gated_linear_kernel<DM>, sgrid, dim3(SCAN_BD), 0, sm, gg, (const float*)m->P, L.n_in, vec4, m->O, ldo)
                     switch (pick_dmax(gg.dim)) {
                         case 32: LP_GLIN(32); break;
                         case 64: LP_GLIN(64); break;
@@ -2963,8 +2965,15 @@ void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want,
             else project_in(nullptr, L.norm2, L.w_up, L.n_up, m->P, L.n_up, EPI_STORE);
             const unsigned nb = (unsigned)(((size_t)R * L.d.ff + 255) / 256);
             if (L.d.ff_kind == B200_FF_CLAMPED_GLU) {
-                if (m->f32) launch(m, lp_clamped_glu_kernel<float>, dim3(nb), dim3(256), 0, ffP, ff_ld, (float*)m->act_a, L.d.ff, R, L.d.ff_limit, L.d.ff_slope);
-                else launch(m, lp_clamped_glu_kernel<bf16>, dim3(nb), dim3(256), 0, ffP, ff_ld, (bf16*)m->act_a, L.d.ff, R, L.d.ff_limit, L.d.ff_slope);
+                const bool v4 = L.d.ff % 4 == 0 && ff_ld % 4 == 0 && ((uintptr_t)ffP & 15) == 0;
+                const unsigned nb4 = (unsigned)(((size_t)R * (L.d.ff / 4) + 255) / 256);
+                if (m->f32) {
+                    if (v4) launch(m, lp_clamped_glu_kernel<float, 4>, dim3(nb4), dim3(256), 0, ffP, ff_ld, (float*)m->act_a, L.d.ff, R, L.d.ff_limit, L.d.ff_slope);
+                    else launch(m, lp_clamped_glu_kernel<float, 1>, dim3(nb), dim3(256), 0, ffP, ff_ld, (float*)m->act_a, L.d.ff, R, L.d.ff_limit, L.d.ff_slope);
+                } else {
+                    if (v4) launch(m, lp_clamped_glu_kernel<bf16, 4>, dim3(nb4), dim3(256), 0, ffP, ff_ld, (bf16*)m->act_a, L.d.ff, R, L.d.ff_limit, L.d.ff_slope);
+                    else launch(m, lp_clamped_glu_kernel<bf16, 1>, dim3(nb), dim3(256), 0, ffP, ff_ld, (bf16*)m->act_a, L.d.ff, R, L.d.ff_limit, L.d.ff_slope);
+                }
             } else {
                 if (m->f32) launch(m, lp_gated_gelu_kernel<float>, dim3(nb), dim3(256), 0, ffP, ff_ld, (float*)m->act_a, L.d.ff, R);
                 else launch(m, lp_gated_gelu_kernel<bf16>, dim3(nb), dim3(256), 0, ffP, ff_ld, (bf16*)m->act_a, L.d.ff, R);

@@ -6,17 +6,27 @@
 // ------------------------------------------------------------------------------------------------ gated linear memory
 // Per (run, head): S [dim][vdim] f32.  With q = silu(zq), f = l + (1 - l) sigmoid(zf + b) per key channel:
 //   S <- diag(f) S + (1 - f) v^T,   o = S^T q          (the forget gate also says how much of v is written).
-// Laid out like the library's other scans: thread column j of S, the column cut into 16-channel pieces over neighbouring lanes,
-// tokens staged a chunk at a time, gates worked out once per (token, channel) in shared memory before the serial loop.
+// lp_glin_gates_kernel turns the pre-activations zq, zf of all rows into q and f in place (once per row and channel: every block of
+// the scan would otherwise repeat it for its few columns); the scan is laid out like the library's other scans: thread column j of
+// S, the column cut into 16-channel pieces over neighbouring lanes, tokens staged a chunk at a time with 16-byte copies.
 // State block of a run: S [H][dim][vdim].
 struct GlinGeom {
     int H, dim, vdim;
     int q_off, v_off, f_off;   // columns of P
     size_t rec_off;
 };
+__global__ void lp_glin_gates_kernel(float* __restrict__ P, int ldp, GlinGeom g, const float* __restrict__ fb, const float* __restrict__ lower, int R) {
+    const int n = g.H * g.dim;
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)R * n) return;
+    const int r = (int)(i / n), c = (int)(i - (size_t)r * n);
+    float* p = P + (size_t)r * ldp;
+    const float zq = p[g.q_off + c], lo = lower[c];
+    p[g.q_off + c] = zq * sigmoid_f(zq);
+    p[g.f_off + c] = lo + (1.0f - lo) * sigmoid_f(p[g.f_off + c] + fb[c]);
+}
 template <int DMAX>
-__global__ void __launch_bounds__(SCAN_BD) lp_gated_linear_kernel(StepMeta sm, GlinGeom g, const float* __restrict__ P, int ldp,
-                                                                  const float* __restrict__ fb, const float* __restrict__ lower,
+__global__ void __launch_bounds__(SCAN_BD) lp_gated_linear_kernel(StepMeta sm, GlinGeom g, const float* __restrict__ P, int ldp, int vec4,
                                                                   float* __restrict__ O, int ldo) {
     constexpr int CH = ScanChunk<DMAX>::N, SPLIT = DMAX / SCAN_DREG, COLS = SCAN_BD / SPLIT;
     __shared__ __align__(16) float qs[CH][DMAX];
@@ -38,28 +48,33 @@ __global__ void __launch_bounds__(SCAN_BD) lp_gated_linear_kernel(StepMeta sm, G
         (&fs[0][0])[i] = 1.0f;
     }
     const int jc = blockIdx.x * COLS + (tid % COLS);   // the column this thread stages
+    const int d4 = g.dim >> 2;
     for (int c0 = r0; c0 < r1; c0 += CH) {
         const int nt = min(CH, r1 - c0);
         __syncthreads();   // the previous chunk has been consumed
-        for (int t = 0; t < nt; t++) {
-            const float* p = P + (size_t)(c0 + t) * ldp;
-            for (int d = tid; d < g.dim; d += SCAN_BD) {
-                cp_async4(&qs[t][d], p + g.q_off + h * g.dim + d);
-                cp_async4(&fs[t][d], p + g.f_off + h * g.dim + d);
+        if (vec4) {        // (dim, the columns' offsets and the row pitch are multiples of 4 floats)
+            for (int i = tid; i < nt * d4; i += SCAN_BD) {
+                const int t = i / d4, d = (i - t * d4) * 4;
+                const float* p = P + (size_t)(c0 + t) * ldp + h * g.dim + d;
+                cp_async16(smem_u32(&qs[t][d]), p + g.q_off, 16u);
+                cp_async16(smem_u32(&fs[t][d]), p + g.f_off, 16u);
+            }
+        } else {
+            for (int t = 0; t < nt; t++) {
+                const float* p = P + (size_t)(c0 + t) * ldp;
+                for (int d = tid; d < g.dim; d += SCAN_BD) {
+                    cp_async4(&qs[t][d], p + g.q_off + h * g.dim + d);
+                    cp_async4(&fs[t][d], p + g.f_off + h * g.dim + d);
+                }
             }
         }
         for (int t = tid / COLS; t < nt; t += SPLIT) {
             if (jc < g.vdim) cp_async4(&vs[t][tid % COLS], P + (size_t)(c0 + t) * ldp + g.v_off + h * g.vdim + jc);
             else vs[t][tid % COLS] = 0.0f;
         }
-        cp_async_wait_all();   // (a thread turns the pre-activations it has copied itself)
-        for (int t = 0; t < nt; t++)
-            for (int d = tid; d < g.dim; d += SCAN_BD) {
-                const float zq = qs[t][d], lo = lower[h * g.dim + d];
-                qs[t][d] = zq * sigmoid_f(zq);
-                fs[t][d] = lo + (1.0f - lo) * sigmoid_f(fs[t][d] + fb[h * g.dim + d]);
-            }
+        cp_async_wait_all();
         __syncthreads();
+#pragma unroll 2
         for (int t = 0; t < nt; t++) {
             const float v = vs[t][col];
             float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
@@ -92,16 +107,17 @@ __global__ void __launch_bounds__(SCAN_BD) lp_gated_linear_kernel(StepMeta sm, G
 // One state per channel: z = sigmoid(zz + bz), u = zx + bx, c = u + 1/2 (u >= 0) or sigmoid(u) (u < 0), s <- (1 - z) s + z c;
 // out = s * silu(zg) * out_scale in the compute type (the operand of the branch's output projection).  State block of a run: s [width].
 // s_t = a_t s_(t-1) + b_t with a = 1 - z, b = z c is a composition of affine maps, so a run is cut into GU_SEG segments that
-// blockDim.y threads per channel fold on their own (A = prod a, B = the segment's s from s = 0); the carries are then chained in
-// shared memory and every segment is walked once more from its true start.  One token per run (decoding) is one segment.
+// blockDim.y threads per channel fold on their own (A = prod a, B = the segment's s from s = 0, both kept with the per-token (a, b)
+// of short segments in registers); the carries are then chained in shared memory and every segment is walked once more from its
+// true start.  One token per run (decoding) is one segment.
 struct GunitGeom {
     int width;
     int z_off, x_off, g_off;   // columns of P
     size_t rec_off;
 };
-constexpr int GU_CH = 32, GU_SEG = 8;   // channels and segments per block
-__device__ __forceinline__ void gunit_ab(const float* __restrict__ p, const GunitGeom& g, int c, float bz, float bx, float& a, float& b) {
-    const float z = sigmoid_f(p[g.z_off + c] + bz), u = p[g.x_off + c] + bx;
+constexpr int GU_CH = 32, GU_SEG = 32;   // channels and segments per block
+__device__ __forceinline__ void gunit_ab(float zz, float zx, float bz, float bx, float& a, float& b) {
+    const float z = sigmoid_f(zz + bz), u = zx + bx;
     const float cand = u >= 0.0f ? u + 0.5f : sigmoid_f(u);
     a = 1.0f - z;
     b = z * cand;
@@ -118,27 +134,64 @@ __global__ void __launch_bounds__(GU_CH * GU_SEG) lp_gated_unit_kernel(StepMeta 
     const int per = (len + GU_SEG - 1) / GU_SEG;
     const int t0 = min(seg * per, len), t1 = min(t0 + per, len);
     const float bz = live ? zb[c] : 0.0f, bx = live ? xb[c] : 0.0f;
+    const float* pz = P + (size_t)r0 * ldp + g.z_off + c;
+    const float* px = P + (size_t)r0 * ldp + g.x_off + c;
     float A = 1.0f, B = 0.0f;
-    if (live && len > per)   // (a single segment needs no first pass)
-        for (int t = t0; t < t1; t++) {
+    if (live && len > per) {   // (a single segment needs no first pass)
+        int t = t0;
+        for (; t + 4 <= t1; t += 4) {   // four tokens' loads in flight together
+            float zz[4], zx[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                zz[u] = pz[(size_t)(t + u) * ldp];
+                zx[u] = px[(size_t)(t + u) * ldp];
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                float a, b;
+                gunit_ab(zz[u], zx[u], bz, bx, a, b);
+                A *= a;
+                B = fmaf(a, B, b);
+            }
+        }
+        for (; t < t1; t++) {
             float a, b;
-            gunit_ab(P + (size_t)(r0 + t) * ldp, g, c, bz, bx, a, b);
+            gunit_ab(pz[(size_t)t * ldp], px[(size_t)t * ldp], bz, bx, a, b);
             A *= a;
             B = fmaf(a, B, b);
         }
+    }
     As[seg][threadIdx.x] = A;
     Bs[seg][threadIdx.x] = B;
     float s = live ? sg[c] : 0.0f;   // (read before the barrier: the last segment's thread overwrites it after its walk)
     __syncthreads();
     for (int q = 0; q < seg; q++) s = fmaf(As[q][threadIdx.x], s, Bs[q][threadIdx.x]);   // the state at the start of this segment
     if (!live) return;
-    for (int t = t0; t < t1; t++) {
-        const float* p = P + (size_t)(r0 + t) * ldp;
+    const float* pg = P + (size_t)r0 * ldp + g.g_off + c;
+    OutT* po = out + (size_t)r0 * out_ld + c;
+    int t = t0;
+    for (; t + 4 <= t1; t += 4) {
+        float zz[4], zx[4], zg[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            zz[u] = pz[(size_t)(t + u) * ldp];
+            zx[u] = px[(size_t)(t + u) * ldp];
+            zg[u] = pg[(size_t)(t + u) * ldp];
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            float a, b;
+            gunit_ab(zz[u], zx[u], bz, bx, a, b);
+            s = fmaf(a, s, b);
+            po[(size_t)(t + u) * out_ld] = from_f<OutT>(s * zg[u] * sigmoid_f(zg[u]) * out_scale);
+        }
+    }
+    for (; t < t1; t++) {
         float a, b;
-        gunit_ab(p, g, c, bz, bx, a, b);
+        gunit_ab(pz[(size_t)t * ldp], px[(size_t)t * ldp], bz, bx, a, b);
         s = fmaf(a, s, b);
-        const float zg = p[g.g_off + c];
-        out[(size_t)(r0 + t) * out_ld + c] = from_f<OutT>(s * zg * sigmoid_f(zg) * out_scale);
+        const float zg = pg[(size_t)t * ldp];
+        po[(size_t)t * out_ld] = from_f<OutT>(s * zg * sigmoid_f(zg) * out_scale);
     }
     if (seg == (len - 1) / per) sg[c] = s;   // the last segment that holds tokens ends on the run's last state
 }
@@ -169,13 +222,27 @@ __global__ void __launch_bounds__(256) lp_dual_norm_add_kernel(float* __restrict
 }
 
 // ------------------------------------------------------------------------------------------------ clamped gated feed-forward
-// out[r][n] = g sigmoid(slope g) (u + 1), g = min(P[r][n], limit), u = clamp(P[r][ff + n], -limit, limit): P holds [gate | up]
-template <typename OutT>
+// out[r][n] = g sigmoid(slope g) (u + 1), g = min(P[r][n], limit), u = clamp(P[r][ff + n], -limit, limit): P holds [gate | up].
+// A thread takes VEC neighbouring units (VEC = 4: 16-byte loads; ff, the row pitch and the column offset multiples of 4).
+__device__ __forceinline__ float clamped_glu_f(float zg, float zu, float limit, float slope) {
+    const float g = fminf(zg, limit), u = fminf(fmaxf(zu, -limit), limit);
+    return g * sigmoid_f(slope * g) * (u + 1.0f);
+}
+template <typename OutT, int VEC>
 __global__ void lp_clamped_glu_kernel(const float* __restrict__ P, int ldp, OutT* __restrict__ out, int ff, int R, float limit, float slope) {
+    const int per = ff / VEC;
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= (size_t)R * ff) return;
-    const int r = (int)(i / ff), n = (int)(i - (size_t)r * ff);
+    if (i >= (size_t)R * per) return;
+    const int r = (int)(i / per), n = (int)(i - (size_t)r * per) * VEC;
     const float* p = P + (size_t)r * ldp;
-    const float g = fminf(p[n], limit), u = fminf(fmaxf(p[ff + n], -limit), limit);
-    out[i] = from_f<OutT>(g * sigmoid_f(slope * g) * (u + 1.0f));
+    if (VEC == 4) {
+        const float4 a = *reinterpret_cast<const float4*>(p + n), b = *reinterpret_cast<const float4*>(p + ff + n);
+        OutT* o = out + (size_t)r * ff + n;
+        o[0] = from_f<OutT>(clamped_glu_f(a.x, b.x, limit, slope));
+        o[1] = from_f<OutT>(clamped_glu_f(a.y, b.y, limit, slope));
+        o[2] = from_f<OutT>(clamped_glu_f(a.z, b.z, limit, slope));
+        o[3] = from_f<OutT>(clamped_glu_f(a.w, b.w, limit, slope));
+    } else {
+        out[(size_t)r * ff + n] = from_f<OutT>(clamped_glu_f(p[n], p[ff + n], limit, slope));
+    }
 }
