@@ -322,7 +322,7 @@ def main():
     # DRAM traffic per token is an ncu measurement (dram__bytes_read + write of one launch / its tokens): it cannot be taken inside a
     # timed run, so it is read from the capture committed for THIS kernel and labelled with its source; null if there is none
     traffic, traffic_src = None, None
-    for tname in ("r02_stream2_dram_traffic.json", "gemv_dram_traffic.json"):
+    for tname in ("v2_stream2_dram_traffic.json", "gemv_dram_traffic.json"):
         tpath = os.path.join(ROOT, "profiles", tname)
         if os.path.exists(tpath):
             try:

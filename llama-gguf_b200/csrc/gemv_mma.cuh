@@ -7,7 +7,7 @@
 // Fused around it: RMSNorm of x (simd.rs:847-899), +bias (layers.rs:68-74), +residual
 // (layers.rs:1202-1241), silu(gate)*up (simd.rs:598-649), out += w_e*y (moe.rs:363-368).
 //
-// Second generation (profiles/r01_mega_ncu_full.md: the fp16 HMMA version spent 4.1 thread-instructions per
+// Second generation (profiles/v1_mega_ncu_full.md: the fp16 HMMA version spent 4.1 thread-instructions per
 // weight, half of them outside the dot products, and the token was issue-bound):
 //  * the dot products are INTEGER tensor-pipe MMAs (mma.sync.m16n8k32 u8 x s8 -> s32, SASS IMMA.16832):
 //    a 32-bit word of nibbles becomes four A-operand quants with ONE LOP3 (w & 0x0F0F0F0F; the high nibbles are

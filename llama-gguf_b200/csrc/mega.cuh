@@ -1,6 +1,6 @@
 // mega.cuh — one persistent, cooperative kernel per decoded token (or per run of greedy tokens).
 //
-// The graph path launches ~195 kernels per Llama-3-8B token; in-kernel timelines (profiles/r01_v4_gemv_mma.md)
+// The graph path launches ~195 kernels per Llama-3-8B token; in-kernel timelines (profiles/v1_v4_gemv_mma.md)
 // show ~5 us of fixed cost per launch (launch, x staging behind cold loads, merge, exit) against 1.5-10 us of
 // streaming.  Here the token is ONE launch of one CTA per SM; the layer sequence of GpuOnlyInference::forward
 // (src/backend/cuda/gpu_only.rs:849-1010; CPU: model/llama.rs:275-362, layers.rs:1082-1245) becomes a list of

@@ -1,7 +1,7 @@
 // stream.cuh — the streamed per-token megakernel: one persistent CTA per SM whose PRODUCER warp never stops pulling
 // weights from HBM while the consumer warps walk the phases of the token.
 //
-// Why (profiles/r01_mega_ncu_full.md, per-phase timeline): in the first megakernel (mega.cuh) every GEMV phase
+// Why (profiles/v1_mega_ncu_full.md, per-phase timeline): in the first megakernel (mega.cuh) every GEMV phase
 // pays ~5 us of fixed cost (grid barrier, x staging, ring ramp-up, stragglers) against 1.5-10 us of streaming, and
 // HBM idles during all of it: 29 % of the copy roofline for a whole token.  Weights never depend on the token, so
 // here they are fetched by a warp that is not part of any phase:

@@ -1,7 +1,7 @@
 // stream2.cuh — second streamed per-token megakernel: the round-2 decode path.
 //
 // Round 1 (stream.cuh) moved exactly the algorithmic bytes but left HBM idle two thirds of the time
-// (profiles/r01_stream_ncu_full.md): ~4 us of fixed cost per phase (CTA-wide barriers around the grid
+// (profiles/v1_stream_ncu_full.md): ~4 us of fixed cost per phase (CTA-wide barriers around the grid
 // barrier, the staged-x copy, merge + epilogue), whole 32-row tiles per CTA (448 gate/up tiles on 148 CTAs: the four heavy
 // CTAs finish 4.4 us late; 128 O / down tiles leave 20 CTAs idle), 7 consumer warps at 255 registers (1.75 warps per
 // scheduler) and 15.6 us of attention per layer behind six dependent global round trips.  This kernel keeps the idea
