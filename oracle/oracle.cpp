@@ -1,7 +1,7 @@
 // oracle.cpp — CPU restatement of llama-gguf's quantized-forward hot path.
 //
 // TEST INFRASTRUCTURE ONLY.  Nothing under llama-gguf_b200/ may link, import or
-// call this file; it is the *checker* for the CUDA path (tests/, smoke(),
+// call this file; it is what the CUDA path is compared with (tests/, smoke(),
 // bench.py's cpu_baseline / --impl reference leg), never the product.
 //
 // The reference (Lexmata/llama-gguf v0.14.0) is pure Rust and no Rust toolchain
