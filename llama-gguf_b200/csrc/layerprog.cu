@@ -1464,6 +1464,7 @@ struct LpModel {
     float* taps = nullptr;
     size_t taps_floats = 0;
     int taps_len = 0;
+    std::string launch_fail;   // name and launch shape of the first kernel whose launch was refused since the last report
     uint64_t launches = 0, weight_bytes = 0, kv_bytes_per_pos = 0;
     // tensor-core GEMM: on for bf16 steps of at least tc_min_rows rows (B200_LP_TC=0 keeps the CUDA-core kernel); *tc_err is set by a
     // bounded wait that gave up
@@ -1556,6 +1557,17 @@ template <typename... KArgs, typename... Args>
 void launch(LpModel* m, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, Args&&... args) {
     kern<<<grid, block, smem, m->stream>>>(std::forward<Args>(args)...);
     m->launches++;
+    if (m->launch_fail.empty()) {   // the first refused launch is remembered by name, so that the step's error says which kernel it was
+        const cudaError_t e = cudaPeekAtLastError();
+        if (e != cudaSuccess) {
+            const char* name = nullptr;
+            if (cudaFuncGetName(&name, (const void*)kern) != cudaSuccess || !name) name = "?";
+            char buf[512];
+            snprintf(buf, sizeof buf, "%s <<<(%u,%u,%u), (%u,%u,%u), %zu>>>: %s", name, grid.x, grid.y, grid.z, block.x, block.y, block.z, smem,
+                     cudaGetErrorString(e));
+            m->launch_fail = buf;
+        }
+    }
 }
 
 // The tensor-core GEMM takes bf16 operands whose rows are 16-byte aligned (K and the row pitches multiples of 8).
@@ -1615,7 +1627,8 @@ void gemm_t(LpModel* m, const void* X, int ldx, const void* W, int ldw, int N, i
         const int Nall = N * groups;
         dim3 grid(std::min((Nall + 7) / 8, 4 * 148)), block(256);
         const size_t xbytes = (size_t)R * K * sizeof(T);
-        const int stage = (!heads && vec_ok && sizeof(T) * VN == 16 && xbytes <= 48 * 1024) ? 1 : 0;
+        // (40 KB: the kernel's static shared memory counts against the 48 KB a launch gets without opting in)
+        const int stage = (!heads && vec_ok && sizeof(T) * VN == 16 && xbytes <= 40 * 1024) ? 1 : 0;
         const size_t smem = stage ? xbytes : 0;
         const RowsTail tl = tail ? *tail : RowsTail{};
         const int nh = heads ? N : 0;
@@ -2389,7 +2402,7 @@ int lp_finalize(LpModel* m, std::string* err) {
             if (L.d.mixer == B200_MIX_SOFTMAX_ATTN || L.d.mixer == B200_MIX_ATTN_RECURRENT)
                 need = std::max(need, (size_t)(((L.pg.C + 3) & ~3) + L.pg.rot_dims + (L.pg.v_rot ? L.ag.vdim : 0)) * 4);
         if (need > 200 * 1024) return lp_fail(err, B200_ERR_UNSUPPORTED, "softmax mixer: q, k and v of one token exceed 200 KB of shared memory");
-        if (need > 48 * 1024) LCU(cudaFuncSetAttribute(lp_attn_prep2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)need));
+        if (need > 32 * 1024) LCU(cudaFuncSetAttribute(lp_attn_prep2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)need));
     }
     if (p.norm_weight_offset != 0.0f) {   // norm weights stored around zero: (offset + w) once, in f32
         std::vector<std::string> nm = {"final.norm"};
@@ -2427,7 +2440,7 @@ int lp_finalize(LpModel* m, std::string* err) {
     }
     if (p.streams > 0) {   // the stream kernel keeps a row of the width in shared memory
         if ((size_t)p.width * 4 > 200 * 1024) return lp_fail(err, B200_ERR_UNSUPPORTED, "multi-stream form: a row exceeds 200 KB of shared memory");
-        if ((size_t)p.width * 4 > 48 * 1024) {
+        if ((size_t)p.width * 4 > 32 * 1024) {
             const int sb = p.width * 4;
             LCU(cudaFuncSetAttribute(lp_streams_kernel<float, 1, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, sb));
             LCU(cudaFuncSetAttribute(lp_streams_kernel<float, 4, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, sb));
@@ -2720,7 +2733,7 @@ void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want,
         const float* add = m->run_pass[run] >= 0 ? loop_step + (size_t)m->run_pass[run] * W : nullptr;
         // the few-row expert kernels (16-byte loads: sizes multiples of 8 / 4, the rows in shared memory)
         const bool moe_sel_ok = L.d.ff_kind == B200_FF_MOE && m->use_fuse && R <= 2 * GV_ROWS && W % (m->f32 ? 4 : 8) == 0 &&
-                                L.d.moe.expert_ff % (m->f32 ? 4 : 8) == 0 && L.d.moe.shared_ff % (m->f32 ? 4 : 8) == 0 && (size_t)R * W * elt(m) <= 48 * 1024;
+                                L.d.moe.expert_ff % (m->f32 ? 4 : 8) == 0 && L.d.moe.shared_ff % (m->f32 ? 4 : 8) == 0 && (size_t)R * W * elt(m) <= 40 * 1024;
         const LayerPlan* moe_next = ((few || sfew) && moe_sel_ok) ? &L : nullptr;      // the mixer's output kernel also routes
         cur = &L;
         sub = 0;
@@ -3130,6 +3143,7 @@ int lp_step(LpModel* m, int n_runs, const int* seqs, const int* pos0, const int*
             if (graph) cudaGraphDestroy(graph);
             if (e != cudaSuccess) {
                 cudaGetLastError();
+                m->launch_fail.clear();
                 g = LpModel::Graph();
                 m->use_graph = false;          // fall back to eager launches for good
                 m->launches = before;
@@ -3158,7 +3172,14 @@ int lp_step(LpModel* m, int n_runs, const int* seqs, const int* pos0, const int*
     }
     LCU(cudaMemcpyAsync(m->h_tc_err, m->tc_err, sizeof(int), cudaMemcpyDeviceToHost, m->stream));
     LCU(cudaStreamSynchronize(m->stream));
-    LCU(cudaGetLastError());
+    {
+        const cudaError_t e_ = cudaGetLastError();
+        if (e_ != cudaSuccess || !m->launch_fail.empty()) {
+            const std::string what = m->launch_fail.empty() ? std::string(cudaGetErrorString(e_)) : m->launch_fail;
+            m->launch_fail.clear();
+            return lp_fail(err, B200_ERR_OPERATION_FAILED, "b200_step: " + what);
+        }
+    }
     if (*m->h_tc_err) {   // a bounded wait of the tensor-core GEMM gave up: the step's results are void
         const int code = *m->h_tc_err;
         *m->h_tc_err = 0;

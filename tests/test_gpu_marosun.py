@@ -666,6 +666,28 @@ def test_decode_kernels_for_few_rows_against_the_many_row_path(b200, monkeypatch
     assert np.median(d) < 2e-2 and (d < 2e-2).mean() > 0.9
 
 
+@pytest.mark.parametrize("compute,rows", [("float32", 4), ("float32", 3), ("bfloat16", 8), ("bfloat16", 7), ("float32", 16)])
+def test_few_rows_against_wide_matrices(b200, compute, rows):
+    # a handful of rows whose staged copy for a wide output projection (64 heads x 48 = 3072 inputs) or down projection (3072) comes
+    # to exactly, or just under, the shared memory that a launch gets without opting in; more rows than that go unstaged
+    cfg = S.config([S.layer_p(heads=64, kv_heads=8, dim=8, vdim=48, chunk=5, r_heads=2, r_dim=16, r_vdim=24, mlp=S.dense(3072, limit=2.0)),
+                    S.layer_a(heads=2, kv_heads=1, dim=16, vdim=16, r=S.rot(dims=8), mlp=S.moe(experts=4, top=2, ff=16))], width=96, vocab=60)
+    w = S.random_weights(cfg, 81)
+    toks = tokens(2 * rows + 1, cfg["vocab"], 82)
+    want = O.Model(cfg, w).forward(toks)
+    gpu = S.gpu_model(cfg, w, compute)
+    try:
+        got = [gpu.step([(0, toks[:rows])], list(range(rows))), gpu.step([(0, toks[rows:2 * rows])], list(range(rows))),
+               gpu.step([(0, toks[2 * rows:])], [0])]
+        d = np.array([S.rel_err(g, wnt) for g, wnt in zip(np.concatenate(got), want)])
+        if compute == "float32":
+            assert d.max() < F32_TOL
+        else:
+            assert np.median(d) < BF16_TOL and (d < BF16_TOL).mean() > 0.8
+    finally:
+        gpu.close()
+
+
 def test_many_rows_of_experts_in_f32(b200):
     # enough rows for the sorted (token, choice) form: pre-activations, the pair's weight on the input, plain sum of the choices
     cfg = S.config([S.layer_q(mlp=S.moe(experts=5, top=2, ff=24)), S.layer_a(mlp=S.moe(experts=3, top=1, ff=16))])
