@@ -1471,6 +1471,9 @@ struct LpModel {
     bool use_tc = true;
     bool use_fuse = true;        // B200_LP_FUSE=0: every step of a layer as a kernel of its own (norm, projection, ...)
     bool use_attn_tile = true;   // B200_LP_ATTN_TILE=0: the warp kernel for prompts too
+    bool use_glin_seg = true;    // B200_LP_GLIN_SEG=0: the gated linear memory always walks whole runs
+    float* glin_carry = nullptr; // segment carries of the gated linear memory [runs][segments][heads][dim][vdim]
+    size_t glin_carry_bytes = 0;
     bool use_stream_tail = true; // B200_LP_STREAM_TAIL=0: few rows of the multi-stream form launch lp_streams_kernel instead of the fused tails
     // decode steps replay a CUDA graph per (rows, wanted rows, head); a graph is void once a scratch buffer has moved (B200_LP_GRAPH=0: eager)
     struct Graph { cudaGraphExec_t exec = nullptr; uint64_t launches = 0, epoch = 0; bool warm = false; };
@@ -1857,6 +1860,8 @@ int lp_create(const b200_program_desc* prog, const b200_layer_desc* layers, int 
         if (e && *e) m->use_fuse = atoi(e) != 0;
         e = getenv("B200_LP_ATTN_TILE");
         if (e && *e) m->use_attn_tile = atoi(e) != 0;
+        e = getenv("B200_LP_GLIN_SEG");
+        if (e && *e) m->use_glin_seg = atoi(e) != 0;
         e = getenv("B200_LP_STREAM_TAIL");
         if (e && *e) m->use_stream_tail = atoi(e) != 0;
         e = getenv("B200_LP_GRAPH");
@@ -2475,7 +2480,7 @@ void lp_destroy(LpModel* m) {
     for (SlotMem& s : m->slot) { cudaFree(s.kv); cudaFree(s.rec); }
     for (SlotMem& s : m->pool) { cudaFree(s.kv); cudaFree(s.rec); }
     for (void* ptr : {(void*)m->inv_freq, (void*)m->d_meta, (void*)m->x, (void*)m->P, (void*)m->qbuf, (void*)m->O, (void*)m->conv, (void*)m->logits,
-                      m->hn, m->act_a, m->hw, (void*)m->pick, (void*)m->taps, (void*)m->y, (void*)m->vsrc, (void*)m->moe_w, (void*)m->moe_selw,
+                      m->hn, m->act_a, m->hw, (void*)m->pick, (void*)m->taps, (void*)m->glin_carry, (void*)m->y, (void*)m->vsrc, (void*)m->moe_w, (void*)m->moe_selw,
                       (void*)m->moe_sel, (void*)m->moe_pos, (void*)m->moe_seg, m->moe_xp, (void*)m->moe_yp, (void*)m->xs, m->cq, (void*)m->vrot})
         cudaFree(ptr);
     if (m->h_meta) cudaFreeHost(m->h_meta);
@@ -2602,6 +2607,17 @@ bool attn_tile(LpModel* m, const StepMeta& sm, const AttnGeom& ag, int ldp, int 
     if (ag.dim <= 64 && ag.vdim <= 64) return attn_tile_launch<64, 64>(m, sm, ag, ldp, n_runs, max_len);
     if (ag.vdim <= 128) return attn_tile_launch<128, 128>(m, sm, ag, ldp, n_runs, max_len);
     return attn_tile_launch<128, 256>(m, sm, ag, ldp, n_runs, max_len);
+}
+
+// Into how many segments the gated linear memory cuts the runs of a step (1 = whole runs): only long runs, and only while whole runs
+// would leave SMs idle (a block per 16 to 64 columns of a head's state and run); segments of at least 64 tokens.
+int glin_segments(const LpModel* m, int H, int dim, int vdim, int n_runs, int max_len) {
+    if (!m->use_glin_seg || max_len < 256) return 1;
+    const int cols = SCAN_BD / (pick_dmax(dim) / SCAN_DREG);
+    const long blocks = (long)((vdim + cols - 1) / cols) * H * n_runs;
+    if (blocks > 148) return 1;   // (measured: from one block per SM on, the segments' second pass costs what their overlap wins)
+    const long want = (6 * 148 + blocks - 1) / blocks;
+    return (int)std::max<long>(1, std::min<long>(std::min<long>(want, GC_SEG_MAX), max_len / 64));
 }
 
 // The warp kernel: any row count, both compute modes.
@@ -2771,13 +2787,24 @@ void enqueue_step(LpModel* m, const StepMeta& sm, int R, int n_runs, int n_want,
                     dim3 sgrid((gg.vdim + cols - 1) / cols, gg.H, n_runs);
                     const int vec4 = (gg.dim % 4 == 0 && gg.q_off % 4 == 0 && gg.f_off % 4 == 0 && L.n_in % 4 == 0) ? 1 : 0;
                     launch(m, lp_glin_gates_kernel, dim3((unsigned)(((size_t)R * gg.H * gg.dim + 255) / 256)), dim3(256), 0, m->P, L.n_in, gg, L.rec_b0, L.rec_lower, R);
-#define LP_GLIN(DM) launch(m, lp_gated_linear_kernel<DM>, sgrid, dim3(SCAN_BD), 0, sm, gg, (const float*)m->P, L.n_in, vec4, m->O, ldo)
-                    switch (pick_dmax(gg.dim)) {
-                        case 32: LP_GLIN(32); break;
-                        case 64: LP_GLIN(64); break;
-                        case 128: LP_GLIN(128); break;
-                        default: LP_GLIN(256); break;
+                    int nseg = glin_segments(m, gg.H, gg.dim, gg.vdim, n_runs, max_len);
+                    if ((size_t)n_runs * nseg * gg.H * gg.dim * gg.vdim * 4 > m->glin_carry_bytes) nseg = 1;
+#define LP_GLIN(DM, MODE, Z) launch(m, lp_gated_linear_kernel<DM, MODE>, dim3(sgrid.x, sgrid.y, (unsigned)(Z)), dim3(SCAN_BD), 0, sm, gg, (const float*)m->P, L.n_in, vec4, m->O, ldo, nseg, m->glin_carry)
+#define LP_GLIN_ALL(MODE, Z)                                                                                           \
+                    switch (pick_dmax(gg.dim)) {                                                                       \
+                        case 32: LP_GLIN(32, MODE, Z); break;                                                          \
+                        case 64: LP_GLIN(64, MODE, Z); break;                                                          \
+                        case 128: LP_GLIN(128, MODE, Z); break;                                                        \
+                        default: LP_GLIN(256, MODE, Z); break;                                                         \
                     }
+                    if (nseg <= 1) {
+                        LP_GLIN_ALL(0, n_runs)
+                    } else {   // segments fold side by side, their carries are chained, every segment runs from its true start
+                        LP_GLIN_ALL(1, n_runs * (nseg - 1))
+                        launch(m, lp_glin_carry_kernel, dim3(((gg.dim + GC_CH - 1) / GC_CH) * ((gg.vdim + GC_CH - 1) / GC_CH), gg.H, n_runs), dim3(GC_CH * GC_TL), 0, sm, gg, (const float*)m->P, L.n_in, nseg, m->glin_carry);
+                        LP_GLIN_ALL(2, n_runs * nseg)
+                    }
+#undef LP_GLIN_ALL
 #undef LP_GLIN
                     dim3 hgrid(R, (gg.H + 3) / 4);   // per-head unit RMS times the shared weight, no gate
                     if (m->f32) launch(m, lp_headnorm_gate_kernel<float>, hgrid, dim3(128), 0, (const float*)m->O, ldo, (const float*)m->P, L.n_in, 0, L.rec_norm, 1, gg.H, gg.vdim, p.norm_eps, 2, (float*)right, L.k_cat, rscale, R);
@@ -3113,6 +3140,19 @@ int lp_step(LpModel* m, int n_runs, const int* seqs, const int* pos0, const int*
     }
     int max_len = 1;
     for (int i = 0; i < n_runs; i++) max_len = std::max(max_len, lens[i]);
+    {   // segment carries of the gated linear memories, when this step's runs are cut
+        size_t need = 0;
+        for (const LayerPlan& L : m->plan)
+            if (L.d.mixer == B200_MIX_ATTN_RECURRENT && L.d.rec_kind == B200_REC_GATED_LINEAR) {
+                const int nseg = glin_segments(m, L.gl.H, L.gl.dim, L.gl.vdim, n_runs, max_len);
+                if (nseg > 1) need = std::max(need, (size_t)n_runs * nseg * L.gl.H * L.gl.dim * L.gl.vdim * 4);
+            }
+        if (need > m->glin_carry_bytes) {
+            m->glin_carry_bytes = 0;
+            if ((rc = grow(&m->glin_carry, need, err))) return rc;
+            m->glin_carry_bytes = need;
+        }
+    }
     const int head = (n_want > 0 && pick_out) ? 2 : (n_want > 0 && logits_out) ? 1 : 0;
     const int taps_len = m->taps_on ? lens[0] : 0;
     // A decode step (one row per run, every slot already holds state) always launches the same kernels with the same arguments: the

@@ -10,6 +10,12 @@
 // the scan would otherwise repeat it for its few columns); the scan is laid out like the library's other scans: thread column j of
 // S, the column cut into 16-channel pieces over neighbouring lanes, tokens staged a chunk at a time with 16-byte copies.
 // State block of a run: S [H][dim][vdim].
+// Long runs on an otherwise empty GPU are cut into `nseg` segments, because the update is affine in S with a diagonal factor:
+//   MODE 1  every segment but the last folds its tokens from S = 0 into carry[run][seg + 1] (no outputs);
+//   lp_glin_carry_kernel multiplies the forget gates of each segment per channel (D) and chains carry[k + 1] = D_k carry[k] +
+//           carry[k + 1] from carry[0] = the state that earlier steps left, so that carry[k] is the state at the start of segment k;
+//   MODE 2  every segment runs from its carry with outputs, the last one leaves the state.
+// MODE 0 is the whole run in one block per column group (decoding, short runs, many runs).
 struct GlinGeom {
     int H, dim, vdim;
     int q_off, v_off, f_off;   // columns of P
@@ -25,23 +31,34 @@ __global__ void lp_glin_gates_kernel(float* __restrict__ P, int ldp, GlinGeom g,
     p[g.q_off + c] = zq * sigmoid_f(zq);
     p[g.f_off + c] = lo + (1.0f - lo) * sigmoid_f(p[g.f_off + c] + fb[c]);
 }
-template <int DMAX>
+template <int DMAX, int MODE>
 __global__ void __launch_bounds__(SCAN_BD) lp_gated_linear_kernel(StepMeta sm, GlinGeom g, const float* __restrict__ P, int ldp, int vec4,
-                                                                  float* __restrict__ O, int ldo) {
+                                                                  float* __restrict__ O, int ldo, int nseg, float* __restrict__ carry) {
     constexpr int CH = ScanChunk<DMAX>::N, SPLIT = DMAX / SCAN_DREG, COLS = SCAN_BD / SPLIT;
     __shared__ __align__(16) float qs[CH][DMAX];
     __shared__ __align__(16) float fs[CH][DMAX];
     __shared__ float vs[CH][COLS];
     const int tid = threadIdx.x, col = tid / SPLIT, sub = tid % SPLIT;
-    const int j = blockIdx.x * COLS + col, h = blockIdx.y, run = blockIdx.z;
-    const int r0 = sm.run_start[run], r1 = sm.run_start[run + 1];
-    float* Sg = reinterpret_cast<float*>(sm.run_rec[run] + g.rec_off) + (size_t)h * g.dim * g.vdim;
+    const int j = blockIdx.x * COLS + col, h = blockIdx.y;
+    const int zsegs = MODE == 1 ? nseg - 1 : MODE == 2 ? nseg : 1;
+    const int run = blockIdx.z / zsegs, seg = blockIdx.z - run * zsegs;
+    int r0 = sm.run_start[run], r1 = sm.run_start[run + 1];
+    if (MODE != 0) {   // this block's segment of the run (it may be empty)
+        const int sl = (r1 - r0 + nseg - 1) / nseg;
+        r0 = min(r0 + seg * sl, r1);
+        r1 = min(r0 + sl, r1);
+    }
+    const size_t hs = (size_t)g.dim * g.vdim;
+    float* Sg = reinterpret_cast<float*>(sm.run_rec[run] + g.rec_off) + (size_t)h * hs;
+    float* Cin = MODE == 2 ? carry + (((size_t)run * nseg + seg) * g.H + h) * hs : nullptr;
+    float* Sout = MODE == 0 ? Sg : MODE == 1 ? carry + (((size_t)run * nseg + seg + 1) * g.H + h) * hs : (seg == nseg - 1 ? Sg : nullptr);
+    const float* Sin = MODE == 0 ? Sg : Cin;
     const bool live = j < g.vdim;
     float s[SCAN_DREG];
 #pragma unroll
     for (int i = 0; i < SCAN_DREG; i++) {
         const int d = ((i >> 2) * SPLIT + sub) * 4 + (i & 3);   // channel of register i
-        s[i] = (live && d < g.dim) ? Sg[(size_t)d * g.vdim + j] : 0.0f;
+        s[i] = (MODE != 1 && live && d < g.dim) ? Sin[(size_t)d * g.vdim + j] : 0.0f;
     }
     for (int i = tid; i < CH * DMAX; i += SCAN_BD) {   // beyond dim: q = 0 and f = 1, so the padding rows stay zero
         (&qs[0][0])[i] = 0.0f;
@@ -56,14 +73,14 @@ __global__ void __launch_bounds__(SCAN_BD) lp_gated_linear_kernel(StepMeta sm, G
             for (int i = tid; i < nt * d4; i += SCAN_BD) {
                 const int t = i / d4, d = (i - t * d4) * 4;
                 const float* p = P + (size_t)(c0 + t) * ldp + h * g.dim + d;
-                cp_async16(smem_u32(&qs[t][d]), p + g.q_off, 16u);
+                if (MODE != 1) cp_async16(smem_u32(&qs[t][d]), p + g.q_off, 16u);
                 cp_async16(smem_u32(&fs[t][d]), p + g.f_off, 16u);
             }
         } else {
             for (int t = 0; t < nt; t++) {
                 const float* p = P + (size_t)(c0 + t) * ldp;
                 for (int d = tid; d < g.dim; d += SCAN_BD) {
-                    cp_async4(&qs[t][d], p + g.q_off + h * g.dim + d);
+                    if (MODE != 1) cp_async4(&qs[t][d], p + g.q_off + h * g.dim + d);
                     cp_async4(&fs[t][d], p + g.f_off + h * g.dim + d);
                 }
             }
@@ -81,26 +98,76 @@ __global__ void __launch_bounds__(SCAN_BD) lp_gated_linear_kernel(StepMeta sm, G
 #pragma unroll
             for (int i = 0; i < SCAN_DREG; i += 4) {
                 const float4 f4 = *reinterpret_cast<const float4*>(&fs[t][((i >> 2) * SPLIT + sub) * 4]);
-                const float4 q4 = *reinterpret_cast<const float4*>(&qs[t][((i >> 2) * SPLIT + sub) * 4]);
                 s[i] = fmaf(f4.x, s[i] - v, v);
                 s[i + 1] = fmaf(f4.y, s[i + 1] - v, v);
                 s[i + 2] = fmaf(f4.z, s[i + 2] - v, v);
                 s[i + 3] = fmaf(f4.w, s[i + 3] - v, v);
-                a0 = fmaf(s[i], q4.x, a0);
-                a1 = fmaf(s[i + 1], q4.y, a1);
-                a2 = fmaf(s[i + 2], q4.z, a2);
-                a3 = fmaf(s[i + 3], q4.w, a3);
+                if (MODE != 1) {
+                    const float4 q4 = *reinterpret_cast<const float4*>(&qs[t][((i >> 2) * SPLIT + sub) * 4]);
+                    a0 = fmaf(s[i], q4.x, a0);
+                    a1 = fmaf(s[i + 1], q4.y, a1);
+                    a2 = fmaf(s[i + 2], q4.z, a2);
+                    a3 = fmaf(s[i + 3], q4.w, a3);
+                }
             }
-            const float acc = split_sum<SPLIT>((a0 + a1) + (a2 + a3));
-            if (live && sub == 0) O[(size_t)(c0 + t) * ldo + h * g.vdim + j] = acc;
+            if (MODE != 1) {
+                const float acc = split_sum<SPLIT>((a0 + a1) + (a2 + a3));
+                if (live && sub == 0) O[(size_t)(c0 + t) * ldo + h * g.vdim + j] = acc;
+            }
         }
     }
-    if (live)
+    if (live && Sout)
 #pragma unroll
         for (int i = 0; i < SCAN_DREG; i++) {
             const int d = ((i >> 2) * SPLIT + sub) * 4 + (i & 3);
-            if (d < g.dim) Sg[(size_t)d * g.vdim + j] = s[i];
+            if (d < g.dim) Sout[(size_t)d * g.vdim + j] = s[i];
         }
+}
+
+// The carries of a segmented run: block = (32 channels x 32 columns of a head's state, run).  First the product of the forget gates of every segment
+// but the last, per channel (GC_TL threads walk a segment's tokens side by side; the gates are read in rows of 32 channels), then
+// carry[0] = the state, carry[k + 1] = D_k carry[k] + carry[k + 1] over this block's part of the state.
+constexpr int GC_CH = 32, GC_TL = 8, GC_SEG_MAX = 16;
+__global__ void __launch_bounds__(GC_CH * GC_TL) lp_glin_carry_kernel(StepMeta sm, GlinGeom g, const float* __restrict__ P, int ldp, int nseg,
+                                                                      float* __restrict__ carry) {
+    __shared__ float part[GC_TL][GC_CH];
+    __shared__ float D[GC_SEG_MAX][GC_CH];
+    const int lane = threadIdx.x % GC_CH, tl = threadIdx.x / GC_CH;
+    const int vt = (g.vdim + GC_CH - 1) / GC_CH;
+    const int d0 = (blockIdx.x / vt) * GC_CH, v0 = (blockIdx.x % vt) * GC_CH, h = blockIdx.y, run = blockIdx.z;
+    const int r0 = sm.run_start[run], r1 = sm.run_start[run + 1];
+    const int sl = (r1 - r0 + nseg - 1) / nseg;
+    const int d = d0 + lane;
+    for (int k = 0; k + 1 < nseg; k++) {
+        const int a = min(r0 + k * sl, r1), b = min(a + sl, r1);
+        float prod = 1.0f;
+        if (d < g.dim)
+            for (int t = a + tl; t < b; t += GC_TL) prod *= P[(size_t)t * ldp + g.f_off + h * g.dim + d];
+        part[tl][lane] = prod;
+        __syncthreads();
+        if (tl == 0) {
+            float v = part[0][lane];
+#pragma unroll
+            for (int i = 1; i < GC_TL; i++) v *= part[i][lane];
+            D[k][lane] = v;
+        }
+        __syncthreads();
+    }
+    const size_t hs = (size_t)g.dim * g.vdim;
+    const float* Sg = reinterpret_cast<const float*>(sm.run_rec[run] + g.rec_off) + (size_t)h * hs;
+    const int nd = min(GC_CH, g.dim - d0), nv = min(GC_CH, g.vdim - v0);
+    for (int i = threadIdx.x; i < nd * nv; i += GC_CH * GC_TL) {
+        const int dl = i / nv;
+        const size_t at = (size_t)(d0 + dl) * g.vdim + v0 + (i - dl * nv);
+        float* c = carry + ((size_t)run * nseg * g.H + h) * hs + at;
+        const size_t step = (size_t)g.H * hs;
+        float v = Sg[at];
+        c[0] = v;
+        for (int k = 0; k + 1 < nseg; k++) {
+            v = fmaf(D[k][dl], v, c[(size_t)(k + 1) * step]);
+            c[(size_t)(k + 1) * step] = v;
+        }
+    }
 }
 
 // ------------------------------------------------------------------------------------------------ gated unit

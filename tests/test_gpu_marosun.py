@@ -688,6 +688,36 @@ def test_few_rows_against_wide_matrices(b200, compute, rows):
         gpu.close()
 
 
+@pytest.mark.parametrize("dims", [(2, 20, 12), (1, 136, 40), (3, 64, 64)])
+def test_gated_memory_cut_into_segments(b200, monkeypatch, dims):
+    # long runs on an empty GPU are folded segment by segment and chained through carries: a batch of a long run, a run shorter than
+    # the segment count (empty segments) and a middling one, then a second long portion that starts from the state the first left;
+    # against the oracle, and the whole-run kernel (B200_LP_GLIN_SEG=0) against the same
+    heads, dim, vdim = dims
+    cfg = S.config([S.layer_p(chunk=50, r_heads=heads, r_dim=dim, r_vdim=vdim, mlp=None),
+                    S.layer_p(heads=2, kv_heads=1, dim=16, vdim=8, chunk=9, r_heads=heads, r_dim=dim, r_vdim=vdim, left_scale=0.1, right_scale=2.0,
+                              mlp=S.dense(24))], width=48, vocab=64)
+    w = S.random_weights(cfg, 91)
+    # a lower bound near one on half of the channels keeps old tokens alive across many segments
+    for i in range(2):
+        lo = w["l%d.mix.right.lower" % i]
+        lo[::2] = S.round_bf16(np.full_like(lo[::2], 0.99))
+    ref = O.Model(cfg, w)
+    a, b, c = tokens(300 + 280, 64, 92), tokens(3, 64, 93), tokens(131, 64, 94)
+    wa, wb, wc = ref.forward(a), ref.forward(b), ref.forward(c)
+    for seg in ("1", "0"):
+        monkeypatch.setenv("B200_LP_GLIN_SEG", seg)
+        gpu = S.gpu_model(cfg, w, max_seq_len=600)
+        try:
+            g = gpu.step([(0, a[:300]), (1, b), (2, c)], list(range(300 + 3 + 131)))
+            assert S.rel_err(g[:300], wa[:300]) < F32_TOL and S.rel_err(g[300:303], wb) < F32_TOL and S.rel_err(g[303:], wc) < F32_TOL, seg
+            g = gpu.step([(0, a[300:])], list(range(280)))
+            assert S.rel_err(g, wa[300:]) < F32_TOL, seg
+            assert S.rel_err(gpu.decode_batch([1, 2], [5, 6])[0], ref.forward(b + [5])[-1]) < F32_TOL
+        finally:
+            gpu.close()
+
+
 def test_many_rows_of_experts_in_f32(b200):
     # enough rows for the sorted (token, choice) form: pre-activations, the pair's weight on the input, plain sum of the choices
     cfg = S.config([S.layer_q(mlp=S.moe(experts=5, top=2, ff=24)), S.layer_a(mlp=S.moe(experts=3, top=1, ff=16))])
