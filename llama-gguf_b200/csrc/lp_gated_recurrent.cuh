@@ -141,8 +141,10 @@ __global__ void __launch_bounds__(GC_CH * GC_TL) lp_glin_carry_kernel(StepMeta s
     for (int k = 0; k + 1 < nseg; k++) {
         const int a = min(r0 + k * sl, r1), b = min(a + sl, r1);
         float prod = 1.0f;
-        if (d < g.dim)
+        if (d < g.dim) {
+#pragma unroll 4
             for (int t = a + tl; t < b; t += GC_TL) prod *= P[(size_t)t * ldp + g.f_off + h * g.dim + d];
+        }
         part[tl][lane] = prod;
         __syncthreads();
         if (tl == 0) {
@@ -162,11 +164,16 @@ __global__ void __launch_bounds__(GC_CH * GC_TL) lp_glin_carry_kernel(StepMeta s
         float* c = carry + ((size_t)run * nseg * g.H + h) * hs + at;
         const size_t step = (size_t)g.H * hs;
         float v = Sg[at];
+        float fold[GC_SEG_MAX - 1];   // every segment's fold is fetched before the chain starts
+#pragma unroll
+        for (int k = 0; k < GC_SEG_MAX - 1; k++) fold[k] = k + 1 < nseg ? c[(size_t)(k + 1) * step] : 0.0f;
         c[0] = v;
-        for (int k = 0; k + 1 < nseg; k++) {
-            v = fmaf(D[k][dl], v, c[(size_t)(k + 1) * step]);
-            c[(size_t)(k + 1) * step] = v;
-        }
+#pragma unroll
+        for (int k = 0; k < GC_SEG_MAX - 1; k++)
+            if (k + 1 < nseg) {
+                v = fmaf(D[k][dl], v, fold[k]);
+                c[(size_t)(k + 1) * step] = v;
+            }
     }
 }
 
